@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the tree-attention decode operator.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2] [--impl reference]
+
+A step is one call of flash_decoding_attention on one synthetic batch.  At N GPUs every rank
+holds its own batch of the workload's shape (the job's sequences sharded by batch, no
+data-path collective): weak scaling, value = calls all ranks completed per second of the
+slowest rank.  Prints ONE JSON line (rank 0).
+
+Keys beyond the basic contract:
+  roofline      dominant kernel (stage 1): algorithmic KV bytes per launch / its CUDA-event
+                duration, against the measured HBM copy peak
+  cpu_baseline  the fp32 CPU oracle timed on this box's host cores (reported baseline only)
+  e2e           same metric through the public Python call with the step's inputs (q, tree
+                K/V, mask, lengths) copied from pinned host memory and the result copied back
+                inside the timed region; the KV cache, which is decode state that lives in HBM
+                across steps, is resident
+  e2e_cold      as e2e, but the KV cache is shipped from pinned host memory every step too
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_oracle_calls_per_s(w, min_seconds: float, max_calls: int):
+    """Times the fp32 CPU oracle (oracle/tree_attention_oracle.py) on whole calls of the
+    workload, on the host cores torch uses.  Returns (calls/s, calls timed, threads)."""
+    from flash_tree_attn_b200.workloads import make_inputs
+    from oracle.tree_attention_oracle import tree_attention_oracle  # timed CPU baseline
+
+    inp = make_inputs(w, "cpu")
+    args = (inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
+            inp["kv_seq_len"], None, w.G)
+    tree_attention_oracle(*args)  # warm-up (thread pool, allocator)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        tree_attention_oracle(*args)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds or n >= max_calls:
+            break
+    return n / dt, n, torch.get_num_threads()
+
+
+def reference_arm(args, w):
+    """--impl reference: the CPU oracle (a port of the reference's dense checker,
+    flash_tree_attn.py:388-397, ragged- and GQA-aware) on the host cores; the reference's own
+    Python/Triton source is not available on the benchmark machine."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from flash_tree_attn_b200.workloads import make_inputs
+    from oracle.tree_attention_oracle import tree_attention_oracle
+
+    inp = make_inputs(w, "cpu")
+    a = (inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
+         inp["kv_seq_len"], None, w.G)
+    for _ in range(max(1, min(args.warmup, 3))):
+        tree_attention_oracle(*a)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tree_attention_oracle(*a)
+    dt = time.perf_counter() - t0
+    val = args.steps / dt
+    print(json.dumps({
+        "impl": "reference", "metric": "tree_attn_calls_per_s", "value": val, "unit": "calls/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(w, inp["lens"]),
+        "cpu_baseline": {"value": val, "unit": "calls/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{args.steps} whole calls of {w.name} (all {w.B} sequences) on the host cores"},
+        "e2e": {"value": val, "unit": "calls/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(w, lens):
+    return {
+        "workload": f"{w.name}: B={w.B} H={w.H} kv_group_num={w.G} D={w.D} q_len={w.Q} "
+                    f"{str(w.dtype).split('.')[-1]} ctx={w.ctx} lens={w.lens} tree={w.tree} block_size={w.block_size}",
+        "sum_kv_len": int(sum(lens)),
+        "l2": "inputs larger than L2: the KV rows one call streams exceed the 126 MB L2, no flush needed",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default="cfg2")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default=None, choices=[None, "auto", "mma", "umma"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from flash_tree_attn_b200.workloads import WORKLOADS, draw_lengths, flops, kv_bytes, make_inputs, small
+
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, w)
+        return
+
+    import flash_tree_attn_b200 as fta
+    from flash_tree_attn_b200 import _lib
+
+    _lib.load()  # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    if args.kernel:
+        fta.set_kernel(args.kernel)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    # each rank holds its own batch of the workload's shape (the job's batch, sharded)
+    wr = small(w, seed=w.seed + 1000 * rank)
+    lens = draw_lengths(wr)
+    inp = make_inputs(wr, dev, lens=lens)
+    call_args = (inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
+                 inp["kv_seq_len"], w.block_size, w.ctx)
+    prep = fta.prepare(*call_args, kv_group_num=w.G)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-timed region: inputs resident in HBM -------------------------------------
+    for _ in range(args.warmup):
+        prep.run()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        prep.run()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+
+    # ---- dominant kernel alone (stage 1), for the roofline -------------------------------
+    for _ in range(3):
+        prep.run_stage1()
+    torch.cuda.synchronize()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        prep.run_stage1()
+    s1.record()
+    torch.cuda.synchronize()
+    ms_stage1 = s0.elapsed_time(s1) / args.steps
+    m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    m0.record()
+    for _ in range(args.steps):
+        prep.run_stage2()
+    m1.record()
+    torch.cuda.synchronize()
+    ms_stage2 = m0.elapsed_time(m1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public call, per-step inputs from pinned host memory ------
+    names = ["q", "current_k", "current_v", "mask", "kv_seq_len"]
+    host = {n: inp[n].cpu().pin_memory() for n in names}
+    stage = {n: torch.empty_like(inp[n]) for n in names}
+    out_host = torch.empty((w.B, w.H, w.Q, w.D), dtype=w.dtype).pin_memory()
+    h2d = sum(host[n].numel() * host[n].element_size() for n in names)
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step(cold_cache=None):
+        for n in names:
+            stage[n].copy_(host[n], non_blocking=True)
+        k, v = inp["k_cache"], inp["v_cache"]
+        if cold_cache is not None:
+            k.copy_(cold_cache[0], non_blocking=True)
+            v.copy_(cold_cache[1], non_blocking=True)
+        o = fta.flash_decoding_attention(stage["q"], k, v, stage["current_k"], stage["current_v"], stage["mask"],
+                                         stage["kv_seq_len"], w.block_size, w.ctx, kv_group_num=w.G)
+        out_host.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    x0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    x1.record()
+    barrier()
+    ms_e2e = x0.elapsed_time(x1)
+
+    cold = None
+    cache_bytes = 2 * inp["k_cache"].numel() * inp["k_cache"].element_size()
+    if cache_bytes <= 8 << 30:
+        cold_host = (inp["k_cache"].cpu().pin_memory(), inp["v_cache"].cpu().pin_memory())
+        n_cold = max(2, min(args.steps, 10))
+        e2e_step(cold_host)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(n_cold):
+            e2e_step(cold_host)
+        c1.record()
+        barrier()
+        cold = (c0.elapsed_time(c1), n_cold)
+
+    # ---- max over ranks ---------------------------------------------------------------------
+    vals = torch.tensor([ms, ms_stage1, ms_stage2, ms_e2e, cold[0] if cold else 0.0, float(sum(lens))],
+                        dtype=torch.float64, device=dev)
+    if dist is not None:
+        mx = vals.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = vals.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, ms_stage1, ms_stage2, ms_e2e = (float(x) for x in mx[:4])
+        if cold:
+            cold = (float(mx[4]), cold[1])
+        total_len = float(sm[5])
+    else:
+        total_len = float(sum(lens))
+
+    if rank == 0:
+        hbm_peak, tf_peak, peak_src = measured_peaks()
+        kvb = kv_bytes(w, lens)  # this rank's launch
+        all_kvb = 2 * 2 * w.D * w.Hkv * total_len
+        calls_s = world * args.steps / (ms * 1e-3)
+        achieved = kvb / (ms_stage1 * 1e-3) / 1e9
+        line = {
+            "metric": "tree_attn_calls_per_s", "value": calls_s, "unit": "calls/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": str(w.dtype).split(".")[-1].replace("float16", "fp16").replace("bfloat16", "bf16"),
+            "data": "synthetic", "config": workload_config(w, lens),
+            "kv_read_gbs": all_kvb * args.steps / (ms * 1e-3) / 1e9,
+            "kv_read_frac_of_measured_peak": all_kvb * args.steps / (ms * 1e-3) / 1e9 / (hbm_peak * world),
+            "kv_read_frac_of_nominal_8tbs": all_kvb * args.steps / (ms * 1e-3) / 1e9 / (8000.0 * world),
+            "tflops": world * flops(w, lens) * args.steps / (ms * 1e-3) / 1e12,
+            "stage_ms": {"stage1": ms_stage1, "stage2": ms_stage2},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "stage1", "algorithmic_bytes_per_launch": kvb},
+            "e2e": {"value": world * args.steps / (ms_e2e * 1e-3), "unit": "calls/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h,
+                    "note": "per-step inputs (q, tree K/V, mask, lengths) from pinned host memory, result "
+                            "copied back; the KV cache is decode state resident in HBM"},
+            "gpu_launches": prep.launches * args.steps,
+            "clocks": clocks,
+        }
+        if cold:
+            line["e2e_cold"] = {"value": world * cold[1] / (cold[0] * 1e-3), "unit": "calls/s",
+                                "h2d_bytes_per_step": h2d + cache_bytes, "d2h_bytes_per_step": d2h,
+                                "note": "KV cache also copied from pinned host memory every step (PCIe-bound)"}
+        traffic = os.path.join(ROOT, "profiles", "stage1_traffic.json")
+        if os.path.exists(traffic):
+            try:
+                with open(traffic) as f:
+                    t = json.load(f)
+                line["roofline"]["traffic"] = t.get(w.name, {}).get("dram_bytes_per_launch")
+                line["roofline"]["traffic_source"] = t.get(w.name, {}).get("source")
+            except (OSError, ValueError):
+                pass
+        if not args.no_cpu_baseline:
+            v, n, cores = cpu_oracle_calls_per_s(w, 10.0, 200)
+            line["cpu_baseline"] = {"value": v, "unit": "calls/s", "cores": cores, "kind": "port",
+                                    "sample": f"{n} whole calls of {w.name} by the fp32 CPU oracle (>=10 s of CPU work)"}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

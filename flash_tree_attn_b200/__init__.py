@@ -1,0 +1,26 @@
+"""B200-native tree-attention decode: a drop-in for `flash_tree_attn.flash_decoding_attention`.
+
+    from flash_tree_attn_b200 import flash_decoding_attention
+
+The arithmetic lives in libfta.so (hand-written sm_100a CUDA behind the C ABI of
+include/fta.h); build it with `python -m flash_tree_attn_b200.build`.
+"""
+from .op import (  # noqa: F401
+    flash_decoding_attention,
+    flash_decoding_attention_with_lse,
+    merge_partials,
+    prepare,
+    set_grid_override,
+    set_kernel,
+    set_split_mode,
+)
+
+__all__ = [
+    "flash_decoding_attention",
+    "flash_decoding_attention_with_lse",
+    "merge_partials",
+    "prepare",
+    "set_split_mode",
+    "set_kernel",
+    "set_grid_override",
+]

@@ -1,0 +1,239 @@
+// Shared definitions of the stage-1 / stage-2 kernels: tile geometry, the split plan
+// (evaluated identically on host and device) and small PTX helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/fta.h"
+
+#define FTA_TILE 64          // KV rows per tile, both kernel families
+#define FTA_MAX_BATCH 8192   // prefix table lives in shared memory
+#define FTA_LOG2E 1.4426950408889634f
+#define FTA_LN2 0.6931471805599453f
+
+// Geometry of one launch, computed on the host (fta_api.cu: make_geom).
+// A "unit" is one (sequence b, KV head, M tile): the rows of M = G*Q query rows that one
+// thread block multiplies against a stream of KV tiles.  An M tile is rectangular:
+// hpt heads x qpt queries, row r -> (head r / qpt, query r % qpt).
+struct FtaGeom {
+  int R;       // rows of the kernel's M tile (16/32/64 mma, 128 umma)
+  int qpt;     // queries per M tile
+  int hpt;     // heads per M tile
+  int n_qt;    // M tiles along Q
+  int n_gt;    // M tiles along the group's heads
+  int mtiles;  // n_qt * n_gt
+  int U;       // units per sequence = Hkv * mtiles
+  int n_tree;  // tree tiles per unit (0 when the tree is excluded)
+  int grid;    // thread blocks launched (BALANCED: resident blocks)
+  int min_per; // smallest tile range a block is given (BALANCED)
+  int fixed_max_splits; // FIXED: ceil(ctx / split_tokens)
+  int pad_;
+};
+
+// One contiguous piece of one unit, processed by one block without interruption.
+struct FtaSeg {
+  int b;        // sequence
+  int j;        // unit within the sequence: kvh * mtiles + mtile
+  int c0, c1;   // cache rows [c0, c1)
+  int tt0, tt1; // tree tiles [tt0, tt1)
+  int split;    // index of this piece among the unit's pieces
+  int nsplit;   // pieces of the unit (1 -> the block writes the final result itself)
+  int slot;     // BALANCED: workspace slot of the partial
+};
+
+__host__ __device__ __forceinline__ int fta_cdiv(int a, int b) { return (a + b - 1) / b; }
+
+// kv_seq_len[b], clamped to [0, ctx].
+__host__ __device__ __forceinline__ int fta_load_len(const void* lens, int is_i64, int b, int ctx) {
+  long long v = is_i64 ? ((const long long*)lens)[b] : (long long)((const int*)lens)[b];
+  if (v < 0) v = 0;
+  if (v > ctx) v = ctx;
+  return (int)v;
+}
+
+// ---- BALANCED plan ---------------------------------------------------------------------
+// All units' tiles are laid on one line, sequence-major then unit then tile; a unit of
+// sequence b has ut_b = ceil(L_b/64) + n_tree tiles (cache tiles, then tree tiles).
+// pre[b] = sum_{b'<b} ut_b'.  Unit (b, j) starts at U*pre[b] + j*ut_b.  Block c owns
+// the tiles [c*per, (c+1)*per).  A unit cut by k block boundaries has k+1 pieces.
+struct FtaBalanced {
+  const int* pre;  // [B+1]
+  int B, U, n_tree, per;
+  long long total;
+
+  __host__ __device__ static int choose_per(long long total, int grid, int min_per) {
+    long long per = (total + grid - 1) / (grid > 0 ? grid : 1);
+    if (per < min_per) per = min_per;
+    if (per < 1) per = 1;
+    return (int)per;
+  }
+
+  // sequence whose tile range contains line position x (x < total)
+  __host__ __device__ int find_b(long long x) const {
+    int lo = 0, hi = B;  // invariant: U*pre[lo] <= x < U*pre[hi]
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if ((long long)U * pre[mid] <= x) lo = mid; else hi = mid;
+    }
+    return lo;
+  }
+
+  // Piece of block c that starts at line position lin (lin in c's range).  Returns the
+  // line position where the piece ends.
+  __host__ __device__ long long segment_at(int c, long long lin, FtaSeg& s) const {
+    const long long cbeg = (long long)c * per;
+    long long cend = cbeg + per;
+    if (cend > total) cend = total;
+    const int b = find_b(lin);
+    const int ut = pre[b + 1] - pre[b];
+    const long long boff = lin - (long long)U * pre[b];
+    const int j = (int)(boff / ut);
+    const int t0 = (int)(boff - (long long)j * ut);
+    const long long ustart = lin - t0, uend = ustart + ut;
+    const long long send = cend < uend ? cend : uend;
+    const int t1 = t0 + (int)(send - lin);
+    const int nb = ut - n_tree;  // cache tiles of this unit
+    const int cfirst = (int)(ustart / per), clast = (int)((uend - 1) / per);
+    s.b = b;
+    s.j = j;
+    s.c0 = (t0 < nb ? t0 : nb) * FTA_TILE;
+    s.c1 = (t1 < nb ? t1 : nb) * FTA_TILE;  // caller clamps to L_b
+    s.tt0 = (t0 > nb ? t0 : nb) - nb;
+    s.tt1 = (t1 > nb ? t1 : nb) - nb;
+    s.split = c - cfirst;
+    s.nsplit = clast - cfirst + 1;
+    s.slot = 2 * c + (lin == cbeg ? 0 : 1);
+    return send;
+  }
+
+  // For the merge: pieces of unit (b, j) and the slot of piece i.
+  __host__ __device__ int unit_pieces(int b, int j, int& cfirst, long long& ustart) const {
+    const int ut = pre[b + 1] - pre[b];
+    if (ut == 0) { cfirst = 0; ustart = 0; return 0; }
+    ustart = (long long)U * pre[b] + (long long)j * ut;
+    const long long uend = ustart + ut;
+    cfirst = (int)(ustart / per);
+    return (int)((uend - 1) / per) - cfirst + 1;
+  }
+  __host__ __device__ int piece_slot(int cfirst, long long ustart, int i) const {
+    const int c = cfirst + i;
+    // piece i>0 starts exactly at block c's first tile; piece 0 does so only when the
+    // unit itself starts there
+    const bool first_of_block = (i > 0) || (ustart == (long long)c * per);
+    return 2 * c + (first_of_block ? 0 : 1);
+  }
+};
+
+// ---- FIXED plan ------------------------------------------------------------------------
+// Items are (b, j, s), s in [0, fixed_max_splits] ; s < ceil(L_b/split_tokens) is a cache
+// split, s == fixed_max_splits is the tree piece.  Items are dealt round-robin.
+__host__ __device__ __forceinline__ bool fta_fixed_item(const FtaParams& p, const FtaGeom& g,
+                                                        long long item, int L_of_b_plus1_unused,
+                                                        int& b, int& j, int& s) {
+  const int per_unit = g.fixed_max_splits + 1;
+  const long long per_b = (long long)g.U * per_unit;
+  b = (int)(item / per_b);
+  const long long r = item - (long long)b * per_b;
+  j = (int)(r / per_unit);
+  s = (int)(r - (long long)j * per_unit);
+  return b < p.B;
+}
+
+// ---- row <-> (head, query) mapping of an M tile -----------------------------------------
+struct FtaUnit {
+  int kvh, gt, qt;  // KV head, group-tile, query-tile
+};
+__host__ __device__ __forceinline__ FtaUnit fta_unit(const FtaGeom& g, int j) {
+  FtaUnit u;
+  u.kvh = j / g.mtiles;
+  const int mt = j - u.kvh * g.mtiles;
+  u.gt = mt / g.n_qt;
+  u.qt = mt - u.gt * g.n_qt;
+  return u;
+}
+// row r of the unit's tile -> head h and query qi; false if the row is padding
+__host__ __device__ __forceinline__ bool fta_row(const FtaParams& p, const FtaGeom& g,
+                                                 const FtaUnit& u, int r, int& h, int& qi) {
+  const int hh = r / g.qpt;
+  const int qq = r - hh * g.qpt;
+  const int gi = u.gt * g.hpt + hh;
+  qi = u.qt * g.qpt + qq;
+  h = u.kvh * (p.H / p.Hkv) + gi;
+  return hh < g.hpt && gi < (p.H / p.Hkv) && qi < p.Q;
+}
+
+#ifdef __CUDACC__
+// ---- device helpers ----------------------------------------------------------------------
+
+// Block-cooperative build of the prefix table pre[0..B] in shared memory (warp 0 scans).
+// Must be followed by __syncthreads().
+__device__ __forceinline__ void fta_build_prefix(const FtaParams& p, int n_tree, int* pre) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int carry = 0;
+    if (lane == 0) pre[0] = 0;
+    for (int base = 0; base < p.B; base += 32) {
+      const int b = base + lane;
+      int v = 0;
+      if (b < p.B) v = fta_cdiv(fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx), FTA_TILE) + n_tree;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+      }
+      if (b < p.B) pre[b + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+}
+
+__device__ __forceinline__ float fta_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fta_log2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T> struct FtaType;
+template <> struct FtaType<__half> {
+  using T2 = __half2;
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ __half from_float(float a) { return __float2half_rn(a); }
+};
+template <> struct FtaType<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ __nv_bfloat16 from_float(float a) { return __float2bfloat16_rn(a); }
+};
+
+// Store 4 consecutive output values (fp32 in registers) as `out_dtype` at element
+// offset `off` of `base`.  off is a multiple of 4.
+__device__ __forceinline__ void fta_store4(void* base, int out_dtype, long long off, float4 v) {
+  if (out_dtype == FTA_DTYPE_F32) {
+    *reinterpret_cast<float4*>((float*)base + off) = v;
+  } else if (out_dtype == FTA_DTYPE_F16) {
+    uint2 w;
+    w.x = FtaType<__half>::pack(v.x, v.y);
+    w.y = FtaType<__half>::pack(v.z, v.w);
+    *reinterpret_cast<uint2*>((__half*)base + off) = w;
+  } else {
+    uint2 w;
+    w.x = FtaType<__nv_bfloat16>::pack(v.x, v.y);
+    w.y = FtaType<__nv_bfloat16>::pack(v.z, v.w);
+    *reinterpret_cast<uint2*>((__nv_bfloat16*)base + off) = w;
+  }
+}
+#endif  // __CUDACC__

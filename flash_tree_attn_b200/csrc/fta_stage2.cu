@@ -1,0 +1,124 @@
+// Stage 2: log-sum-exp merge of the partial attentions stage 1 left behind, one thread
+// block per unit (sequence, KV head, M tile), float4 along head_dim.
+//
+// It replaces the reference's _flash_decoding_fwd_reduce_kernel (flash_tree_attn.py:146-211)
+// and the final two-way blend with the tree part (flash_tree_attn.py:373).  The recurrence
+// is the reference's (:195-208): m' = max(m, lse_s); acc = acc*e^(m-m') + e^(lse_s-m')*o_s;
+// l = l*e^(m-m') + e^(lse_s-m').  Unlike the reference the LSE stays fp32 throughout (the
+// reference rounds it to the query dtype, :285,:211, before the blend).
+#include "fta_common.cuh"
+
+namespace {
+
+struct Acc {
+  float m, l;
+  float4 a;
+  __device__ __forceinline__ void init() { m = -INFINITY; l = 0.f; a = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void add(float lse, const float4& o) {
+    if (lse == -INFINITY) return;  // an empty partial contributes nothing
+    const float mn = fmaxf(m, lse);
+    const float sc = __expf(m - mn);  // m == -inf -> 0
+    const float w = __expf(lse - mn);
+    a.x = a.x * sc + w * o.x; a.y = a.y * sc + w * o.y;
+    a.z = a.z * sc + w * o.z; a.w = a.w * sc + w * o.w;
+    l = l * sc + w;
+    m = mn;
+  }
+  __device__ __forceinline__ float4 value() const {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    return make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+  }
+  __device__ __forceinline__ float lse() const { return l > 0.f ? m + __logf(l) : -INFINITY; }
+};
+
+constexpr int kThreads = 128;
+
+__global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, const FtaGeom g) {
+  extern __shared__ int pre[];
+  const int b = blockIdx.x / g.U, j = blockIdx.x - b * g.U;
+  const FtaUnit unit = fta_unit(g, j);
+  const int D = p.D, D4 = D >> 2;
+
+  if (p.split_mode == FTA_SPLIT_BALANCED) {
+    fta_build_prefix(p, g.n_tree, pre);
+    __syncthreads();
+    FtaBalanced plan;
+    plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree;
+    plan.total = (long long)g.U * pre[p.B];
+    plan.per = FtaBalanced::choose_per(plan.total, g.grid, g.min_per);
+    int cfirst; long long ustart;
+    const int np = plan.unit_pieces(b, j, cfirst, ustart);
+    if (np == 1) return;  // stage 1 wrote the final rows itself
+    const float* ws_o = reinterpret_cast<const float*>(p.workspace);
+    const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
+    for (int i = threadIdx.x; i < g.R * D4; i += kThreads) {
+      const int row = i / D4, c4 = (i - row * D4) * 4;
+      int h, qi;
+      if (!fta_row(p, g, unit, row, h, qi)) continue;
+      Acc acc; acc.init();
+      for (int s = 0; s < np; ++s) {
+        const long long slot = plan.piece_slot(cfirst, ustart, s);
+        const float lse = ws_l[slot * g.R + row];
+        const float4 o = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row) * D + c4);
+        acc.add(lse, o);
+      }
+      fta_store4(p.out, p.out_dtype, b * p.o_sb + h * p.o_sh + qi * p.o_sq + c4, acc.value());
+      if (c4 == 0 && p.lse) p.lse[b * p.l_sb + h * p.l_sh + qi] = acc.lse();
+    }
+    return;
+  }
+
+  // FIXED: cache partials in mid_o/mid_lse, the tree partial in tree_o/tree_lse
+  const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx);
+  const int np = fta_cdiv(Lb, p.split_tokens);
+  for (int i = threadIdx.x; i < g.R * D4; i += kThreads) {
+    const int row = i / D4, c4 = (i - row * D4) * 4;
+    int h, qi;
+    if (!fta_row(p, g, unit, row, h, qi)) continue;
+    Acc acc; acc.init();
+    const float* mo = p.mid_o + b * p.mo_sb + h * p.mo_sh + qi * p.mo_sq + c4;
+    const float* ml = p.mid_lse + b * p.ml_sb + h * p.ml_sh + qi;
+    for (int s = 0; s < np; ++s)
+      acc.add(ml[s * p.ml_ss], *reinterpret_cast<const float4*>(mo + s * p.mo_ss));
+    if (p.out_cache)
+      fta_store4(p.out_cache, p.dtype, b * p.oc_sb + h * p.oc_sh + qi * p.oc_sq + c4, acc.value());
+    if (g.n_tree > 0) {
+      const long long ro = ((long long)b * p.H + h) * p.Q + qi;
+      acc.add(p.tree_lse[ro], *reinterpret_cast<const float4*>(p.tree_o + ro * D + c4));
+    }
+    fta_store4(p.out, p.out_dtype, b * p.o_sb + h * p.o_sh + qi * p.o_sq + c4, acc.value());
+    if (c4 == 0 && p.lse) p.lse[b * p.l_sb + h * p.l_sh + qi] = acc.lse();
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) merge_parts_kernel(const FtaMergeParams p) {
+  const int D4 = p.D >> 2;
+  const long long n = (long long)p.rows * D4;
+  for (long long i = (long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += (long long)gridDim.x * kThreads) {
+    const long long row = i / D4;
+    const int c4 = (int)(i - row * D4) * 4;
+    Acc acc; acc.init();
+    for (int s = 0; s < p.n_parts; ++s)
+      acc.add(p.part_lse[s * p.pl_ss + row],
+              *reinterpret_cast<const float4*>(p.part_o + s * p.po_ss + row * p.D + c4));
+    fta_store4(p.out, p.out_dtype, row * p.D + c4, acc.value());
+    if (c4 == 0 && p.lse) p.lse[row] = acc.lse();
+  }
+}
+
+}  // namespace
+
+cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
+  const size_t smem = p.split_mode == FTA_SPLIT_BALANCED ? (size_t)(p.B + 1) * sizeof(int) : 0;
+  stage2_kernel<<<p.B * g.U, kThreads, smem, st>>>(p, g);
+  return cudaGetLastError();
+}
+
+cudaError_t fta_launch_merge_parts(const FtaMergeParams& p, cudaStream_t st) {
+  const long long n = (long long)p.rows * (p.D >> 2);
+  long long blocks = (n + kThreads - 1) / kThreads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  merge_parts_kernel<<<(int)blocks, kThreads, 0, st>>>(p);
+  return cudaGetLastError();
+}

@@ -1,0 +1,366 @@
+"""Host side of the operator: the reference's Python interface over the C-ABI library.
+
+`flash_decoding_attention` keeps the reference's signature, argument meaning, return value
+and assertion behaviour (flash_tree_attn.py:216-376) so that it can be imported in its
+place.  All arithmetic happens in libfta.so; torch is used for device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import FtaParams
+
+_DT = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+
+# "balanced": planner-chosen splits (default).  "block": one partial per `block_size` rows
+# written to mid_output / mid_output_lse exactly where the reference writes them
+# (flash_tree_attn.py:124-144), for callers or tests that read those buffers.
+_split_mode = os.environ.get("FTA_SPLIT_MODE", "balanced")
+_kernel = {"auto": _lib.KERNEL_AUTO, "mma": _lib.KERNEL_MMA, "umma": _lib.KERNEL_UMMA}[
+    os.environ.get("FTA_KERNEL", "auto")
+]
+_grid_override = int(os.environ.get("FTA_GRID", "0"))
+
+_scratch = {}  # (device index, stream, tag) -> tensor, grown on demand
+_ws_bytes_cache = {}
+
+
+def set_split_mode(mode: str) -> None:
+    """"balanced" or "block" (see module docstring)."""
+    global _split_mode
+    if mode not in ("balanced", "block"):
+        raise ValueError(mode)
+    _split_mode = mode
+
+
+def set_kernel(name: str) -> None:
+    """Force a stage-1 kernel family: "auto", "mma" (warp MMA) or "umma" (tcgen05)."""
+    global _kernel
+    _kernel = {"auto": _lib.KERNEL_AUTO, "mma": _lib.KERNEL_MMA, "umma": _lib.KERNEL_UMMA}[name]
+
+
+def set_grid_override(n: int) -> None:
+    """Number of stage-1 thread blocks (0 = planner's choice); results must not depend on it."""
+    global _grid_override
+    _grid_override = int(n)
+
+
+def _scratch_buf(dev: torch.device, stream: int, tag: str, nbytes: int) -> torch.Tensor:
+    key = (dev.index, stream, tag)
+    t = _scratch.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        _scratch[key] = t
+    return t
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+    if t.stride(-1) != 1 or t.data_ptr() % 16:
+        return False
+    return all(s % 8 == 0 for s in t.stride()[:-1])
+
+
+def _mask_strides(mask: torch.Tensor, B: int, H: int, Q: int):
+    """fp32 additive mask -> (tensor, stride_b, stride_h, stride_q); 0 broadcasts.
+
+    Accepted shapes: [Q,Q], [B,Q,Q], [B,1,Q,Q], [B,H,Q,Q] (and size-1 broadcast dims), the
+    set that broadcasts against the reference's [B,H,Q,Q] scores (flash_tree_attn.py:368)
+    plus the 3-D per-sequence form.
+    """
+    if mask.dtype != torch.float32 or mask.stride(-1) != 1:
+        mask = mask.float().contiguous()
+    if mask.dim() == 2:
+        sb = sh = 0
+    elif mask.dim() == 3:
+        sb, sh = (mask.stride(0) if mask.size(0) > 1 else 0), 0
+        assert mask.size(0) in (1, B), "mask batch dimension does not match q"
+    elif mask.dim() == 4:
+        sb = mask.stride(0) if mask.size(0) > 1 else 0
+        sh = mask.stride(1) if mask.size(1) > 1 else 0
+        assert mask.size(0) in (1, B) and mask.size(1) in (1, H), "mask does not broadcast against [B,H,Q,Q]"
+    else:
+        raise AssertionError("mask must have 2, 3 or 4 dimensions")
+    assert mask.size(-1) == Q and mask.size(-2) == Q, "mask must be [.., q_len, q_len]"
+    return mask, sb, sh, mask.stride(-2)
+
+
+class PreparedCall:
+    """One validated call: the filled C-ABI parameter block, its output tensors and the
+    stream it was prepared for.  `run()` launches it (again); the tensors it points at may
+    be overwritten in place between runs.  Used by the benchmark to time the stages apart
+    and by callers that want to pay validation once per shape."""
+
+    __slots__ = ("p", "out", "lse", "stream", "_keep", "launches")
+
+    def __init__(self, p, out, lse, stream, keep):
+        self.p, self.out, self.lse, self.stream, self._keep = p, out, lse, stream, keep
+        self.launches = 2  # stage 1 + stage 2
+
+    def run(self):
+        _lib.check(_lib.load().fta_decode(C.byref(self.p), self.stream), "fta_decode")
+        return self.out, self.lse
+
+    def run_stage1(self):
+        _lib.check(_lib.load().fta_stage1(C.byref(self.p), self.stream), "fta_stage1")
+
+    def run_stage2(self):
+        _lib.check(_lib.load().fta_stage2(C.byref(self.p), self.stream), "fta_stage2")
+
+
+def prepare(
+    q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size=64, max_seq_len_in_batch=None,
+    output=None, mid_output=None, mid_output_lse=None, sm_scale=None, kv_group_num=1, *,
+    want_lse=False, out_dtype=None, with_tree=True,
+) -> PreparedCall:
+    """Validate the arguments of flash_decoding_attention and build the C-ABI call without
+    launching it."""
+    lib = _lib.load()
+    if not q.is_cuda:
+        raise RuntimeError("flash_decoding_attention runs on CUDA tensors only (no CPU path exists)")
+    B, H, Q, D = q.shape
+    Q = int(Q)
+
+    # the reference's own asserts (flash_tree_attn.py:263-268)
+    assert D in {32, 64, 128, 256}
+    assert k_cache.size(-2) == v_cache.size(-2), "Got incompatible block size on kv caches:\n"
+    assert block_size in {16, 32, 64, 128}
+    assert q.dtype in (torch.float16, torch.bfloat16), "q must be fp16 or bf16"
+    assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "kv cache dtype must equal q dtype"
+    G = int(kv_group_num)
+    assert G >= 1 and H % G == 0, "num_heads must be a multiple of kv_group_num"
+    Hkv = H // G
+    assert k_cache.size(0) >= B and k_cache.size(1) == Hkv, "k_cache must be [bsz, num_kv_heads, ctx, head_dim]"
+
+    sm_scale = 1.0 / (D ** 0.5) if sm_scale is None else float(sm_scale)
+    ctx = int(k_cache.size(-2))
+    if max_seq_len_in_batch is not None:
+        ctx = min(ctx, int(max_seq_len_in_batch))
+    # For compatibility with the reference's buffer contract (flash_tree_attn.py:274)
+    max_len = ctx if max_seq_len_in_batch is None else int(max_seq_len_in_batch)
+    kv_max_split_num = (max_len + block_size - 1) // block_size
+
+    if mid_output is not None or mid_output_lse is not None:
+        assert mid_output is not None and mid_output_lse is not None
+        assert (
+            mid_output.size(2) == mid_output_lse.size(2) >= kv_max_split_num
+        ), "Incompatible kv split number of intermediate output tensors"
+        assert (
+            mid_output.size(0) == mid_output_lse.size(0) >= B
+        ), "Incompatible first dimension of output tensors"
+    if output is not None:
+        assert output.size(0) == B, "Incompatible first dimension of output tensors"
+
+    dev = q.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    if not _rows_ok(q):
+        q = q.contiguous()
+    if not _rows_ok(k_cache):
+        k_cache = k_cache.contiguous()
+    if not _rows_ok(v_cache):
+        v_cache = v_cache.contiguous()
+    if kv_seq_len.dtype not in (torch.int32, torch.int64) or not kv_seq_len.is_contiguous():
+        kv_seq_len = kv_seq_len.to(torch.int64).contiguous()
+    if kv_seq_len.device != dev:
+        kv_seq_len = kv_seq_len.to(dev)
+
+    p = FtaParams()
+    p.q = q.data_ptr(); p.q_sb, p.q_sh, p.q_sq = q.stride(0), q.stride(1), q.stride(2)
+    p.k_cache = k_cache.data_ptr(); p.k_sb, p.k_sh, p.k_st = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+    p.v_cache = v_cache.data_ptr(); p.v_sb, p.v_sh, p.v_st = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
+    p.kv_seq_len = kv_seq_len.data_ptr()
+    p.len_is_i64 = 1 if kv_seq_len.dtype == torch.int64 else 0
+    p.cur_head_mul = 1
+    keep = [q, k_cache, v_cache, kv_seq_len]
+
+    if with_tree:
+        assert current_k.dtype == q.dtype and current_v.dtype == q.dtype
+        assert current_k.size(2) == Q and current_v.size(2) == Q, "current_k/current_v must hold q_len rows"
+        hk = current_k.size(1)
+        assert hk in (Hkv, H) and current_v.size(1) == hk, "current_k/current_v must have num_kv_heads or num_heads heads"
+        if not _rows_ok(current_k):
+            current_k = current_k.contiguous()
+        if not _rows_ok(current_v):
+            current_v = current_v.contiguous()
+        # [B,H,Q,D] inputs under GQA: head kvh*G of the group is read (the reference's own
+        # tail needs the heads replicated per group, flash_tree_attn.py:367,371)
+        p.cur_head_mul = G if (hk == H and G > 1) else 1
+        p.cur_k = current_k.data_ptr(); p.ck_sb, p.ck_sh, p.ck_st = current_k.stride(0), current_k.stride(1), current_k.stride(2)
+        p.cur_v = current_v.data_ptr(); p.cv_sb, p.cv_sh, p.cv_st = current_v.stride(0), current_v.stride(1), current_v.stride(2)
+        mask, msb, msh, msq = _mask_strides(mask.to(dev) if mask.device != dev else mask, B, H, Q)
+        p.mask = mask.data_ptr(); p.m_sb, p.m_sh, p.m_sq = msb, msh, msq
+        keep += [current_k, current_v, mask]
+
+    out_dtype = q.dtype if out_dtype is None else out_dtype
+    out = torch.empty((B, H, Q, D), dtype=out_dtype, device=dev)
+    p.out = out.data_ptr(); p.o_sb, p.o_sh, p.o_sq = out.stride(0), out.stride(1), out.stride(2)
+    lse = None
+    if want_lse:
+        lse = torch.empty((B, H, Q), dtype=torch.float32, device=dev)
+        p.lse = lse.data_ptr(); p.l_sb, p.l_sh = lse.stride(0), lse.stride(1)
+
+    p.B, p.H, p.Hkv, p.Q, p.D, p.ctx = B, H, Hkv, Q, D, ctx
+    p.dtype = _DT[q.dtype]
+    p.out_dtype = _DT[out_dtype]
+    p.sm_scale = sm_scale
+    p.with_tree = 1 if with_tree else 0
+    p.kernel = _kernel
+    p.grid_override = _grid_override
+
+    block_mode = _split_mode == "block"
+    if output is None and not block_mode:
+        # planner-balanced splits, fixed-size workspace
+        p.split_mode = _lib.SPLIT_BALANCED
+        key = (dev.index, B, H, Hkv, Q, D, p.dtype, _kernel, _grid_override)
+        nbytes = _ws_bytes_cache.get(key)
+        if nbytes is None:
+            nbytes = lib.fta_workspace_bytes(C.byref(p))
+            if nbytes < 0:
+                raise _lib.FtaError(-nbytes, "fta_workspace_bytes")
+            _ws_bytes_cache[key] = nbytes
+        ws = _scratch_buf(dev, stream, "ws", nbytes)
+        p.workspace = ws.data_ptr(); p.workspace_bytes = ws.numel()
+        keep.append(ws)
+    else:
+        # one partial per split: the reference's buffer layout (flash_tree_attn.py:276-281)
+        p.split_mode = _lib.SPLIT_FIXED
+        if block_mode:
+            split = block_size
+        else:
+            grid = max(lib.fta_plan_grid(C.byref(p)), 1)
+            units = B * Hkv * max(1, (G * Q + 127) // 128)
+            split = max(256, -(-(units * max(ctx, 1)) // (grid * 4)))
+            split = min(-(-split // 64) * 64, max(64, -(-ctx // 64) * 64))
+        p.split_tokens = split
+        S = max(1, -(-ctx // split))
+        use_caller_mid = (
+            block_mode and mid_output is not None and mid_output.dtype == torch.float32
+            and mid_output_lse.dtype == torch.float32 and mid_output.stride(-1) == 1
+            and mid_output_lse.stride(-1) == 1 and mid_output.data_ptr() % 16 == 0
+            and all(s % 4 == 0 for s in mid_output.stride()[:-1])
+            and tuple(mid_output.shape[1:]) == (H, mid_output.size(2), Q, D)
+        )
+        if use_caller_mid:
+            mo, ml = mid_output, mid_output_lse
+        else:
+            mo = _scratch_buf(dev, stream, "mid_o", B * H * S * Q * D * 4).view(torch.float32)[: B * H * S * Q * D].view(B, H, S, Q, D)
+            ml = _scratch_buf(dev, stream, "mid_l", B * H * S * Q * 4).view(torch.float32)[: B * H * S * Q].view(B, H, S, Q)
+        p.mid_o = mo.data_ptr(); p.mo_sb, p.mo_sh, p.mo_ss, p.mo_sq = mo.stride(0), mo.stride(1), mo.stride(2), mo.stride(3)
+        p.mid_lse = ml.data_ptr(); p.ml_sb, p.ml_sh, p.ml_ss = ml.stride(0), ml.stride(1), ml.stride(2)
+        p.mid_splits = int(mo.size(2))
+        keep += [mo, ml]
+        if with_tree:
+            to = _scratch_buf(dev, stream, "tree_o", B * H * Q * D * 4)
+            tl = _scratch_buf(dev, stream, "tree_l", B * H * Q * 4)
+            p.tree_o = to.data_ptr(); p.tree_lse = tl.data_ptr()
+            keep += [to, tl]
+        if output is not None:
+            assert output.dtype == q.dtype and tuple(output.shape) == (B, H, Q, D) and output.stride(-1) == 1
+            p.out_cache = output.data_ptr()
+            p.oc_sb, p.oc_sh, p.oc_sq = output.stride(0), output.stride(1), output.stride(2)
+            keep.append(output)
+
+    return PreparedCall(p, out, lse, stream, keep)
+
+
+def _decode(*args, **kw) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    return prepare(*args, **kw).run()
+
+
+def flash_decoding_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    current_k: torch.Tensor,
+    current_v: torch.Tensor,
+    mask: torch.Tensor,
+    kv_seq_len: torch.Tensor,
+    block_size: int = 64,
+    max_seq_len_in_batch: int = None,
+    output: torch.Tensor = None,
+    mid_output: torch.Tensor = None,
+    mid_output_lse: torch.Tensor = None,
+    sm_scale: int = None,
+    kv_group_num: int = 1,
+):
+    """Tree-attention verification step of speculative decoding (drop-in for the
+    reference's flash_decoding_attention, flash_tree_attn.py:216-376).
+
+    Args:
+        q: [bsz, num_heads, q_len, head_dim] fp16/bf16, the tree nodes' queries.
+        k_cache, v_cache: [bsz, num_kv_heads, ctx, head_dim] dense right-padded caches; rows at
+            or past kv_seq_len[b] are never read.
+        current_k, current_v: [bsz, num_kv_heads, q_len, head_dim] (or num_heads heads,
+            replicated per group) keys/values of the tree nodes, not yet in the cache.
+        mask: additive float mask over the tree nodes, [q_len,q_len], [bsz,q_len,q_len],
+            [bsz,1,q_len,q_len] or [bsz,num_heads,q_len,q_len]; it is ADDED to the scaled
+            scores (flash_tree_attn.py:368), so allowed entries may be any finite value.
+        kv_seq_len: [bsz] int32/int64 cache lengths (tree tokens not included).
+        block_size: reference's split size; here it only sizes the mid buffers' contract,
+            unless split mode "block" is selected (`set_split_mode`).
+        max_seq_len_in_batch: upper bound of kv_seq_len; never read from the device here,
+            so the call does not synchronise (the reference does `.max().item()`, :272).
+        output: optional [bsz, num_heads, q_len, head_dim] buffer; as in the reference it
+            receives the CACHE-ONLY attention (:340-365), not the returned tensor.
+        mid_output, mid_output_lse: optional fp32 scratch in the reference's shapes
+            (:276-281); validated as the reference does (:286-291), written only in split
+            mode "block".
+        sm_scale: defaults to 1/sqrt(head_dim) (:271).
+        kv_group_num: query heads per KV head; head h reads KV head h // kv_group_num (:71).
+
+    Returns:
+        A new tensor [bsz, num_heads, q_len, head_dim] of q's dtype (:373-376).
+    """
+    out, _ = _decode(
+        q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size, max_seq_len_in_batch,
+        output, mid_output, mid_output_lse, sm_scale, kv_group_num,
+        want_lse=False, out_dtype=None, with_tree=True,
+    )
+    return out
+
+
+def flash_decoding_attention_with_lse(
+    q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size=64, max_seq_len_in_batch=None,
+    output=None, mid_output=None, mid_output_lse=None, sm_scale=None, kv_group_num=1,
+    *, out_dtype: Optional[torch.dtype] = None, with_tree: bool = True,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same operator, also returning the fp32 natural-log LSE [bsz, num_heads, q_len] of the
+    merged softmax.  `out_dtype=torch.float32` keeps the result unrounded and
+    `with_tree=False` leaves the tree tokens out: together they give the (O, LSE) partial of
+    one KV-range shard, to be merged across shards (see dist.py).  The reference keeps its
+    LSE internal and in 16 bits (flash_tree_attn.py:285,:373).
+    """
+    return _decode(
+        q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size, max_seq_len_in_batch,
+        output, mid_output, mid_output_lse, sm_scale, kv_group_num,
+        want_lse=True, out_dtype=out_dtype, with_tree=with_tree,
+    )
+
+
+def merge_partials(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype: torch.dtype = torch.float32):
+    """LSE-merge n normalised partial attentions: part_o [n, rows.., D] fp32, part_lse
+    [n, rows..] fp32 -> (out [rows.., D], lse [rows..]).  Used after the all-gather of
+    KV-range shards; restates the reference's stage-2 recurrence (flash_tree_attn.py:195-208).
+    """
+    lib = _lib.load()
+    assert part_o.is_cuda and part_o.dtype == torch.float32 and part_lse.dtype == torch.float32
+    n, D = part_o.size(0), part_o.size(-1)
+    part_o = part_o.contiguous()
+    part_lse = part_lse.contiguous()
+    rows = part_lse[0].numel()
+    assert part_o[0].numel() == rows * D
+    out = torch.empty(part_o.shape[1:], dtype=out_dtype, device=part_o.device)
+    lse = torch.empty(part_lse.shape[1:], dtype=torch.float32, device=part_o.device)
+    mp = _lib.FtaMergeParams()
+    mp.part_o = part_o.data_ptr(); mp.po_ss = rows * D
+    mp.part_lse = part_lse.data_ptr(); mp.pl_ss = rows
+    mp.n_parts, mp.rows, mp.D, mp.out_dtype = n, rows, D, _DT[out_dtype]
+    mp.out = out.data_ptr(); mp.lse = lse.data_ptr()
+    stream = torch.cuda.current_stream(part_o.device).cuda_stream
+    _lib.check(lib.fta_merge_parts(C.byref(mp), stream), "fta_merge_parts")
+    return out, lse

@@ -1,0 +1,199 @@
+/*
+ * fta.h — C ABI of the B200 tree-attention decode library (libfta.so).
+ *
+ * One operator is exported: the tree-attention verification step of speculative
+ * decoding.  Q tree queries per (sequence, head) attend densely to a right-padded
+ * per-sequence KV cache of kv_seq_len[b] rows and, under an additive [Q,Q] mask, to
+ * the Q new tree tokens; both parts are folded into one softmax.
+ *
+ * The entry points replace, for a caller that binds native code, the body of the
+ * reference's only public function
+ *     flash_decoding_attention(q, k_cache, v_cache, current_k, current_v, mask,
+ *                              kv_seq_len, block_size, max_seq_len_in_batch, output,
+ *                              mid_output, mid_output_lse, sm_scale, kv_group_num)
+ * (flash_tree_attn.py:216-376), i.e. its two Triton launches (flash_tree_attn.py:301-334
+ * and :340-365), the eager-torch tree tail (:367-371) and the final LSE blend (:373).
+ *
+ * Conventions: plain pointers and sizes, no C++ or torch types.  All pointers are
+ * device pointers unless a name ends in _host.  Strides are in ELEMENTS.  Every tensor
+ * must have unit stride in its last (head_dim) dimension.  Every call is asynchronous
+ * on the stream it is given, allocates nothing, never synchronises and never throws;
+ * the return value is 0 or an FTA_E_* code (fta_strerror gives the text).
+ */
+#ifndef FTA_H_
+#define FTA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FTA_VERSION 100
+
+/* ---- error codes ------------------------------------------------------------------- */
+#define FTA_OK 0
+#define FTA_E_BADARG 1      /* a size, stride, dtype or pointer is invalid          */
+#define FTA_E_UNSUPPORTED 2 /* a valid request this build has no kernel for         */
+#define FTA_E_WORKSPACE 3   /* workspace / mid buffers too small for the plan       */
+#define FTA_E_CUDA 4        /* a CUDA runtime or driver call failed                 */
+#define FTA_E_TOO_LARGE 5   /* request exceeds the static scratch of fta_*_static   */
+
+/* ---- enums ------------------------------------------------------------------------- */
+#define FTA_DTYPE_F16 0
+#define FTA_DTYPE_BF16 1
+#define FTA_DTYPE_F32 2 /* only as out_dtype */
+
+/* how KV rows are divided among thread blocks */
+#define FTA_SPLIT_BALANCED 0 /* equal tile ranges per resident block (planner)          */
+#define FTA_SPLIT_FIXED 1    /* one partial per split_tokens rows, like the reference's  \
+                                one-program-per-block grid (flash_tree_attn.py:295-299)  */
+
+/* which stage-1 kernel family runs */
+#define FTA_KERNEL_AUTO 0
+#define FTA_KERNEL_MMA 1  /* warp-level mma.sync tiles, cp.async ring                    */
+#define FTA_KERNEL_UMMA 2 /* tcgen05 tiles with TMEM accumulators, TMA ring              */
+
+/*
+ * One call of the operator.  Shapes (reference docstring, flash_tree_attn.py:236-243,
+ * corrected by its index arithmetic :60-94):
+ *   q          [B, H,   Q,   D]            query rows of the tree nodes
+ *   k_cache    [B, Hkv, ctx, D]            dense right-padded cache (v_cache alike)
+ *   current_k  [B, Hkv, Q,   D]            keys of the tree nodes (current_v alike);
+ *                                          cur_head_mul selects head kvh*cur_head_mul,
+ *                                          so a [B,H,Q,D] tensor is passed with mul = G
+ *   mask       fp32, additive, indexed mask[b*m_sb + h*m_sh + i*m_sq + j]; a stride of 0
+ *              broadcasts (flash_tree_attn.py:368 adds it to the scaled scores)
+ *   kv_seq_len [B] int32 or int64 (flash_tree_attn.py:55)
+ * G = H / Hkv consecutive query heads share KV head h / G (flash_tree_attn.py:71).
+ */
+typedef struct FtaParams {
+  /* inputs */
+  const void* q;
+  int64_t q_sb, q_sh, q_sq;
+  const void* k_cache;
+  int64_t k_sb, k_sh, k_st;
+  const void* v_cache;
+  int64_t v_sb, v_sh, v_st;
+  const void* cur_k;
+  int64_t ck_sb, ck_sh, ck_st;
+  const void* cur_v;
+  int64_t cv_sb, cv_sh, cv_st;
+  const float* mask;
+  int64_t m_sb, m_sh, m_sq;
+  const void* kv_seq_len;
+  int32_t len_is_i64;
+  int32_t cur_head_mul;
+
+  /* outputs */
+  void* out; /* [B,H,Q,D] merged attention, out_dtype */
+  int64_t o_sb, o_sh, o_sq;
+  void* out_cache; /* optional: cache-only attention (what the reference leaves in its
+                      `output` argument, flash_tree_attn.py:340-365); q dtype; FIXED only */
+  int64_t oc_sb, oc_sh, oc_sq;
+  float* lse; /* optional [B,H,Q] fp32 natural-log LSE of the merged softmax */
+  int64_t l_sb, l_sh;
+
+  /* partial results.  BALANCED: `workspace` of fta_workspace_bytes() bytes.
+     FIXED: mid_o [B,H,S,Q,D] / mid_lse [B,H,S,Q] fp32 exactly as the reference lays them
+     out (flash_tree_attn.py:276-281), slot s = rows [s*split_tokens,(s+1)*split_tokens);
+     tree_o [B,H,Q,D] / tree_lse [B,H,Q] fp32 contiguous hold the tree-token partial. */
+  void* workspace;
+  int64_t workspace_bytes;
+  float* mid_o;
+  int64_t mo_sb, mo_sh, mo_ss, mo_sq;
+  float* mid_lse;
+  int64_t ml_sb, ml_sh, ml_ss;
+  int32_t mid_splits; /* S: slots available per (b,h) */
+  float* tree_o;
+  float* tree_lse;
+
+  /* sizes */
+  int32_t B, H, Hkv, Q, D, ctx;
+  int32_t dtype;     /* FTA_DTYPE_F16 | FTA_DTYPE_BF16: q, caches, current k/v */
+  int32_t out_dtype; /* dtype of `out`: same as dtype, or FTA_DTYPE_F32 */
+  float sm_scale;
+
+  /* plan */
+  int32_t split_mode;   /* FTA_SPLIT_* */
+  int32_t split_tokens; /* FIXED: rows per split, a multiple of 16 */
+  int32_t with_tree;    /* 0: cache only (a KV-range shard that does not own the tree) */
+  int32_t kernel;       /* FTA_KERNEL_* */
+  int32_t grid_override; /* 0 = planner's choice; else resident blocks to launch (tests) */
+  int32_t reserved_;
+} FtaParams;
+
+/*
+ * Merge of `n_parts` already-normalised partial attentions (used after the all-gather of
+ * KV-range shards): out = sum_s w_s * part_o[s], w_s = softmax_s(part_lse[s]).
+ *   part_o   fp32, part_o[s*po_ss + row*D + d], row in [0, rows)
+ *   part_lse fp32, part_lse[s*pl_ss + row]
+ * It restates flash_tree_attn.py:195-208 for a fixed split count.
+ */
+typedef struct FtaMergeParams {
+  const float* part_o;
+  int64_t po_ss;
+  const float* part_lse;
+  int64_t pl_ss;
+  int32_t n_parts;
+  int32_t rows;
+  int32_t D;
+  int32_t out_dtype; /* FTA_DTYPE_* */
+  void* out;         /* [rows, D] contiguous */
+  float* lse;        /* optional [rows] */
+} FtaMergeParams;
+
+/* Library / ABI version (FTA_VERSION).  No counterpart in the reference. */
+int fta_version(void);
+
+/* Text for an FTA_E_* code.  No counterpart in the reference (it raises AssertionError,
+   flash_tree_attn.py:263-291). */
+const char* fta_strerror(int code);
+
+/* Last CUDA error text seen by this thread inside the library (for FTA_E_CUDA). */
+const char* fta_last_cuda_error(void);
+
+/*
+ * Bytes of `workspace` a BALANCED call with these sizes needs on the current device.
+ * Replaces the reference's per-call torch.empty of mid_output / mid_output_lse
+ * (flash_tree_attn.py:276-281); unlike those it does not grow with B or ctx.
+ * Only B, H, Hkv, Q, D, dtype, kernel and grid_override are read.
+ */
+int64_t fta_workspace_bytes(const FtaParams* p);
+
+/*
+ * The whole operator: stage 1 (split-KV partial attention with the tree-masked tail
+ * fused in) and stage 2 (LSE merge), replacing flash_tree_attn.py:301-376.
+ * `stream` is a cudaStream_t.
+ */
+int fta_decode(const FtaParams* p, void* stream);
+
+/* Stage 1 alone (flash_tree_attn.py:301-334 plus the tail :367-371). */
+int fta_stage1(const FtaParams* p, void* stream);
+
+/* Stage 2 alone (flash_tree_attn.py:340-365 plus the blend :373). */
+int fta_stage2(const FtaParams* p, void* stream);
+
+/* Merge of gathered shard partials (flash_tree_attn.py:195-208 on a fixed split count). */
+int fta_merge_parts(const FtaMergeParams* p, void* stream);
+
+/*
+ * Host-side evaluation of the BALANCED plan, for tests and tooling: given lengths on
+ * the host, report how stage 1 will cut the work.  kv_seq_len_host: [B] int64.
+ * segs_out: up to max_segs rows of 8 int64 each
+ *   {block, b, unit_in_b, cache_row_begin, cache_row_end, tree_tile_begin, tree_tile_end,
+ *    split_index * 65536 + n_splits}.
+ * Returns the number of segments (may exceed max_segs; only max_segs are written) or a
+ * negative FTA_E_* code.  Replaces the reference's implicit plan "one program per
+ * block_size rows" (flash_tree_attn.py:269-274,295-299).
+ */
+int64_t fta_plan_host(const FtaParams* p, const int64_t* kv_seq_len_host, int64_t* segs_out,
+                      int64_t max_segs, int32_t* grid_out, int32_t* per_out);
+
+/* Number of stage-1 thread blocks a call with these sizes launches on the current device. */
+int fta_plan_grid(const FtaParams* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTA_H_ */

@@ -1,0 +1,128 @@
+"""CPU: the C-ABI library loads, exports every symbol include/fta.h declares, and its host
+logic (argument validation, the split plan) behaves.  No kernel is launched."""
+import ctypes as C
+import os
+import random
+import re
+
+import pytest
+
+from flash_tree_attn_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fta.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fta_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(fta_lib):
+    names = declared_symbols()
+    assert "fta_decode" in names and "fta_plan_host" in names
+    for n in names:
+        assert hasattr(fta_lib, n), f"{n} declared in include/fta.h but not exported"
+        assert n in _lib.SYMBOLS, f"{n} has no ctypes prototype"
+
+
+def test_version_and_strerror(fta_lib):
+    assert fta_lib.fta_version() == 100
+    assert fta_lib.fta_strerror(0) == b"ok"
+    for code in range(1, 6):
+        assert len(fta_lib.fta_strerror(code)) > 3
+
+
+def test_struct_layout_matches_header():
+    # sizes printed by a C++ compile of include/fta.h
+    assert C.sizeof(_lib.FtaParams) == 472
+    assert C.sizeof(_lib.FtaMergeParams) == 64
+
+
+def _params(B, H, Hkv, Q, D, ctx, grid, with_tree=1, kernel=_lib.KERNEL_MMA):
+    p = _lib.FtaParams()
+    p.B, p.H, p.Hkv, p.Q, p.D, p.ctx = B, H, Hkv, Q, D, ctx
+    p.dtype = p.out_dtype = _lib.DTYPE_F16
+    p.with_tree = with_tree
+    p.kernel = kernel
+    p.grid_override = grid
+    return p
+
+
+def test_decode_rejects_bad_arguments(fta_lib):
+    p = _params(2, 8, 8, 8, 48, 128, 4)  # head_dim outside {32,64,128,256}
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+    p = _params(2, 8, 3, 8, 64, 128, 4)  # H not a multiple of Hkv
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+    p = _params(2, 8, 8, 8, 64, 128, 4)  # null pointers
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+    assert fta_lib.fta_decode(None, None) == _lib.FTA_E_BADARG
+
+
+def plan(fta_lib, lens, H, Hkv, Q, D, grid, with_tree=1):
+    B = len(lens)
+    p = _params(B, H, Hkv, Q, D, max(lens + [1]), grid, with_tree)
+    arr = (C.c_int64 * B)(*lens)
+    cap = 1 << 16
+    segs = (C.c_int64 * (cap * 8))()
+    g, per = C.c_int32(), C.c_int32()
+    n = fta_lib.fta_plan_host(C.byref(p), arr, segs, cap, C.byref(g), C.byref(per))
+    assert 0 <= n <= cap
+    rows = [tuple(segs[i * 8:(i + 1) * 8]) for i in range(n)]
+    return rows, g.value, per.value
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_balanced_plan_covers_every_tile_once(fta_lib, seed):
+    rng = random.Random(seed)
+    B = rng.choice([1, 2, 5, 32, 128])
+    G = rng.choice([1, 4, 8])
+    Hkv = rng.choice([1, 2, 8])
+    Q = rng.choice([1, 4, 26, 64, 100])
+    lens = [rng.choice([0, 1, 63, 64, 65, rng.randint(1, 5000)]) for _ in range(B)]
+    grid = rng.choice([1, 7, 148, 296])
+    rows, g, per = plan(fta_lib, lens, Hkv * G, Hkv, Q, 128, grid)
+    assert g == grid and per >= 2
+    M = G * Q
+    R = 16 if M <= 16 else 32 if M <= 32 else 64
+    qpt = min(Q, R)
+    hpt = min(G, R // qpt)
+    U = Hkv * (-(-Q // qpt)) * (-(-G // hpt))
+    n_tree = -(-Q // 64)
+    seen_cache, seen_tree, pieces, slots = {}, {}, {}, set()
+    per_block = {}
+    for (c, b, j, c0, c1, t0, t1, packed) in rows:
+        split, nsplit = packed >> 16, packed & 0xFFFF
+        assert 0 <= b < B and 0 <= j < U and 0 <= split < nsplit
+        assert c0 % 64 == 0 and c0 <= max(c0, c1) and c1 <= lens[b]
+        for r in range(c0, c1):
+            seen_cache[(b, j, r)] = seen_cache.get((b, j, r), 0) + 1
+        for t in range(t0, t1):
+            seen_tree[(b, j, t)] = seen_tree.get((b, j, t), 0) + 1
+        pieces.setdefault((b, j), []).append((split, nsplit))
+        per_block[c] = per_block.get(c, 0) + (-(-max(c1 - c0, 0) // 64)) + (t1 - t0)
+    for b in range(B):
+        for j in range(U):
+            for r in range(lens[b]):
+                assert seen_cache.get((b, j, r)) == 1
+            for t in range(n_tree):
+                assert seen_tree.get((b, j, t)) == 1
+            ps = sorted(pieces[(b, j)])
+            assert [s for s, _ in ps] == list(range(ps[0][1])), "split indices of a unit are 0..n-1"
+    assert len(seen_cache) == sum(lens) * U
+    # balance: no block gets more than `per` tiles
+    assert max(per_block.values()) <= per
+
+
+def test_plan_is_balanced_for_ragged_batch(fta_lib):
+    rng = random.Random(5)
+    lens = [rng.randint(16, 16384) for _ in range(128)]
+    rows, g, per = plan(fta_lib, lens, 32, 32, 4, 128, 296)
+    total = sum(-(-L // 64) + 1 for L in lens) * 32
+    assert per == -(-total // 296)
+    # at most two cut pieces per block, so partial slots 2*block + {0,1} never collide
+    cut = {}
+    for (c, b, j, c0, c1, t0, t1, packed) in rows:
+        if (packed & 0xFFFF) > 1:
+            cut[c] = cut.get(c, 0) + 1
+    assert max(cut.values()) <= 2

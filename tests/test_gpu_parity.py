@@ -1,0 +1,303 @@
+"""GPU: the CUDA path (through the C ABI) against the fp32 oracle, the reference-output
+fixtures and the reference restatement.  Tolerances are the ones the operator is specified
+to: max-abs 2e-3 on fp16/bf16 outputs and 1e-3 on the LSE, both against an fp32 evaluation
+of the same masked attention."""
+import pytest
+import torch
+
+from conftest import GOLDEN, load_golden
+
+pytestmark = pytest.mark.gpu
+
+OUT_TOL = 2e-3
+LSE_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def fta():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import flash_tree_attn_b200 as m
+    from flash_tree_attn_b200 import _lib
+
+    _lib.load()  # raises if libfta.so is absent: there is no fallback to test
+    yield m
+    m.set_split_mode("balanced")
+    m.set_kernel("auto")
+    m.set_grid_override(0)
+
+
+def _oracle(inp, G, with_tree=True):
+    from oracle.tree_attention_oracle import tree_attention_oracle
+
+    return tree_attention_oracle(inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"],
+                                 inp["mask"], inp["kv_seq_len"], None, G, with_tree=with_tree)
+
+
+def _run(fta, inp, G, block_size=64, ctx=None, **kw):
+    return fta.flash_decoding_attention_with_lse(
+        inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
+        inp["kv_seq_len"], block_size, ctx, kv_group_num=G, **kw)
+
+
+def _check(out, lse, ora, tag=""):
+    assert out.dtype in (torch.float16, torch.bfloat16, torch.float32)
+    eo = (out.float() - ora["out"]).abs().max().item()
+    el = (lse - ora["lse"]).abs().max().item()
+    assert torch.isfinite(out.float()).all(), tag
+    assert eo <= OUT_TOL, f"{tag}: out max-abs {eo}"
+    assert el <= LSE_TOL, f"{tag}: lse max-abs {el}"
+    return eo, el
+
+
+def _workload(**kw):
+    from flash_tree_attn_b200.workloads import Workload
+
+    base = dict(name="t", B=2, H=8, G=1, D=128, Q=8, dtype=torch.float16, ctx=256, lens="fixed:200,37",
+                tree="random", seed=99)
+    base.update(kw)
+    return Workload(**base)
+
+
+@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_fixtures(fta, name, kernel):
+    fta.set_kernel(kernel)
+    g = load_golden(name)
+    inp = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in g.items()}
+    out, lse = _run(fta, inp, g["kv_group_num"], g["block_size"])
+    ora = _oracle(inp, g["kv_group_num"])
+    _check(out, lse, ora, name)
+    # and against what the reference itself returned for these inputs (its own error included)
+    assert (out.float() - inp["ref_out"].float()).abs().max().item() <= 3e-3
+    # the drop-in entry point returns the same tensor
+    out2 = fta.flash_decoding_attention(inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"],
+                                        inp["mask"], inp["kv_seq_len"], g["block_size"], kv_group_num=g["kv_group_num"])
+    assert out2.dtype == inp["q"].dtype and out2.shape == inp["q"].shape
+    assert torch.equal(out2, out)
+
+
+SHAPES = [
+    # (B, H, G, D, Q, ctx, lens)
+    (2, 8, 1, 64, 8, 128, "fixed:100,37"),
+    (3, 4, 1, 128, 4, 512, "fixed:16,500,129"),
+    (2, 8, 4, 128, 26, 1024, "fixed:1000,333"),
+    (2, 4, 1, 128, 64, 1024, "fixed:1024,700"),
+    (1, 16, 8, 128, 64, 2048, "fixed:2048"),
+    (2, 4, 2, 32, 16, 256, "fixed:255,64"),
+    (1, 2, 1, 256, 16, 256, "fixed:130"),
+    (2, 2, 1, 128, 128, 512, "fixed:512,65"),
+    (5, 6, 3, 64, 7, 320, "fixed:1,63,64,65,320"),
+    (2, 2, 1, 128, 100, 256, "fixed:256,10"),
+]
+
+
+@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_shapes_against_oracle(fta, shape, dtype, kernel):
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel(kernel)
+    B, H, G, D, Q, ctx, lens = shape
+    w = _workload(B=B, H=H, G=G, D=D, Q=Q, ctx=ctx, lens=lens, dtype=dtype, scale=0.5 if dtype == torch.bfloat16 else 1.0)
+    inp = make_inputs(w, "cuda")
+    out, lse = _run(fta, inp, G, ctx=ctx)
+    _check(out, lse, _oracle(inp, G), str(shape))
+
+
+@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("grid", [1, 3, 37, 148, 1000])
+def test_result_independent_of_split_count(fta, grid, kernel):
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel(kernel)
+    w = _workload(B=3, H=8, G=2, D=128, Q=32, ctx=2048, lens="fixed:2048,900,3")
+    inp = make_inputs(w, "cuda")
+    ora = _oracle(inp, 2)
+    fta.set_grid_override(grid)
+    out, lse = _run(fta, inp, 2)
+    fta.set_grid_override(0)
+    _check(out, lse, ora, f"grid={grid}")
+
+
+@pytest.mark.parametrize("kernel", ["mma", "auto"])
+def test_padding_rows_are_never_read(fta, kernel):
+    """NaN in every cache row at or past kv_seq_len must not reach the result (the reference
+    needs finite padding, flash_tree_attn.py:93-94)."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel(kernel)
+    w = _workload(B=2, H=4, G=1, D=128, Q=64, ctx=512, lens="fixed:301,64")
+    inp = make_inputs(w, "cuda", pad_value=float("nan"))
+    out, lse = _run(fta, inp, 1)
+    clean = dict(inp)
+    clean["k_cache"] = torch.nan_to_num(inp["k_cache"], nan=0.0)
+    clean["v_cache"] = torch.nan_to_num(inp["v_cache"], nan=0.0)
+    _check(out, lse, _oracle(clean, 1), "nan padding")
+
+
+def test_zero_length_sequence_is_tree_only(fta):
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    w = _workload(B=2, H=4, G=1, D=64, Q=8, ctx=128, lens="fixed:0,77")
+    inp = make_inputs(w, "cuda")
+    out, lse = _run(fta, inp, 1)
+    ora = _oracle(inp, 1)
+    _check(out, lse, ora, "L=0")
+    assert (out[0].float() - ora["tree_out"][0]).abs().max().item() <= OUT_TOL
+
+
+def test_int64_lengths_and_strided_views(fta):
+    """The reference's benchmark passes sliced cache views (flash_tree_attn.py:483) and its
+    test int64 lengths (:434)."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    w = _workload(B=2, H=4, G=1, D=128, Q=16, ctx=384, lens="fixed:256,100")
+    inp = make_inputs(w, "cuda")
+    big_k = torch.randn(2, 4, 384 + 16, 128, device="cuda").half()
+    big_v = torch.randn(2, 4, 384 + 16, 128, device="cuda").half()
+    inp["k_cache"], inp["current_k"] = big_k[:, :, :384], big_k[:, :, 384:]
+    inp["v_cache"], inp["current_v"] = big_v[:, :, :384], big_v[:, :, 384:]
+    inp["kv_seq_len"] = inp["kv_seq_len"].long()
+    assert not inp["k_cache"].is_contiguous()
+    out, lse = _run(fta, inp, 1)
+    _check(out, lse, _oracle(inp, 1), "strided")
+
+
+@pytest.mark.parametrize("mask_kind", ["2d", "3d", "4d_b1", "4d_bh", "ones"])
+def test_mask_forms(fta, mask_kind):
+    """Additive mask semantics: any finite allowed value is added (the reference's test uses
+    1.0, flash_tree_attn.py:409), and every broadcastable shape is accepted."""
+    from flash_tree_attn_b200.workloads import ancestor_mask, make_inputs, tree_parents
+
+    w = _workload(B=2, H=4, G=2, D=64, Q=16, ctx=128, lens="fixed:128,50")
+    inp = make_inputs(w, "cuda")
+    m = ancestor_mask(tree_parents("random", 16, 3), 1.0 if mask_kind == "ones" else 0.0).cuda()
+    if mask_kind == "3d":
+        m = torch.stack([m, ancestor_mask(tree_parents("random", 16, 4)).cuda()])
+    elif mask_kind == "4d_b1":
+        m = torch.stack([m, ancestor_mask(tree_parents("random", 16, 5)).cuda()])[:, None]
+    elif mask_kind == "4d_bh":
+        m = torch.stack([torch.stack([ancestor_mask(tree_parents("random", 16, 10 * b + h)) for h in range(4)])
+                         for b in range(2)]).cuda()
+        m = m + 0.25 * torch.isfinite(m) * torch.randn_like(m).nan_to_num(0.0)
+        m = torch.where(torch.isnan(m), torch.full_like(m, float("-inf")), m)
+    inp["mask"] = m
+    out, lse = _run(fta, inp, 2)
+    _check(out, lse, _oracle(inp, 2), mask_kind)
+
+
+def test_current_kv_with_all_query_heads(fta):
+    """current_k/v given with num_heads heads, replicated per group, as the reference's tail
+    requires under GQA (flash_tree_attn.py:367)."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    w = _workload(B=2, H=8, G=4, D=128, Q=8, ctx=128, lens="fixed:128,9")
+    inp = make_inputs(w, "cuda")
+    ora = _oracle(inp, 4)
+    inp["current_k"] = inp["current_k"].repeat_interleave(4, dim=1)
+    inp["current_v"] = inp["current_v"].repeat_interleave(4, dim=1)
+    out, lse = _run(fta, inp, 4)
+    _check(out, lse, ora, "expanded current kv")
+
+
+@pytest.mark.parametrize("kernel", ["mma", "auto"])
+def test_output_argument_receives_cache_only_attention(fta, kernel):
+    """Like the reference, `output` ends up holding the cache-only attention and the
+    returned tensor is a different one (flash_tree_attn.py:340-376)."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel(kernel)
+    w = _workload(B=2, H=4, G=1, D=128, Q=16, ctx=1024, lens="fixed:1000,130")
+    inp = make_inputs(w, "cuda")
+    output = torch.full((2, 4, 16, 128), float("nan"), dtype=torch.float16, device="cuda")
+    out, lse = _run(fta, inp, 1, output=output)
+    ora = _oracle(inp, 1)
+    _check(out, lse, ora, "with output")
+    assert out.data_ptr() != output.data_ptr()
+    assert (output.float() - ora["cache_out"]).abs().max().item() <= OUT_TOL
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_block_mode_fills_mid_buffers_like_the_reference(fta, name):
+    """Split mode "block": mid_output / mid_output_lse hold one partial per block_size rows
+    exactly where the reference's stage 1 writes them (flash_tree_attn.py:124-144), slots
+    past a sequence stay untouched, and `output` holds the stage-2 result."""
+    g = load_golden(name)
+    inp = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in g.items()}
+    B, H, Q, D = inp["q"].shape
+    bs = g["block_size"]
+    S = inp["ref_mid_o"].shape[2]
+    mid_o = torch.full((B, H, S, Q, D), float("nan"), device="cuda")
+    mid_l = torch.full((B, H, S, Q), float("nan"), device="cuda")
+    output = torch.zeros((B, H, Q, D), dtype=inp["q"].dtype, device="cuda")
+    fta.set_split_mode("block")
+    try:
+        out, lse = _run(fta, inp, g["kv_group_num"], bs, ctx=S * bs, output=output, mid_output=mid_o,
+                        mid_output_lse=mid_l)
+    finally:
+        fta.set_split_mode("balanced")
+    _check(out, lse, _oracle(inp, g["kv_group_num"]), name + " block mode")
+    for b, L in enumerate(inp["kv_seq_len"].tolist()):
+        n = (L + bs - 1) // bs
+        assert (mid_o[b, :, :n] - inp["ref_mid_o"][b, :, :n]).abs().max().item() <= 1e-3
+        assert (mid_l[b, :, :n] - inp["ref_mid_lse"][b, :, :n]).abs().max().item() <= 1e-3
+        assert torch.isnan(mid_o[b, :, n:]).all() and torch.isnan(mid_l[b, :, n:]).all()
+    assert (output.float() - inp["ref_output"].float()).abs().max().item() <= OUT_TOL
+
+
+def test_reference_assertions_are_kept(fta):
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    w = _workload(B=2, H=4, G=1, D=64, Q=8, ctx=128, lens="fixed:128,50")
+    inp = make_inputs(w, "cuda")
+    a = (inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"], inp["kv_seq_len"])
+    with pytest.raises(AssertionError):
+        fta.flash_decoding_attention(*a, 48)  # block_size outside {16,32,64,128}
+    with pytest.raises(AssertionError):
+        fta.flash_decoding_attention(a[0], a[1], a[2][:, :, :64], *a[3:])  # cache length mismatch
+    with pytest.raises(AssertionError):
+        small = torch.empty(2, 4, 1, 8, 64, device="cuda")
+        fta.flash_decoding_attention(*a, 64, 128, None, small, torch.empty(2, 4, 1, 8, device="cuda"))
+    with pytest.raises(AssertionError):
+        bad = inp["q"][..., :48]
+        fta.flash_decoding_attention(bad, *a[1:])  # head_dim outside {32,64,128,256}
+
+
+@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("cfg,B", [("cfg2", 8), ("cfg3", 8), ("cfg4", 1), ("cfg5", 16)])
+def test_benchmark_shapes(fta, cfg, B, kernel):
+    """The benchmark configurations at full per-sequence size (batch reduced where the
+    caches would not fit a quick test)."""
+    from flash_tree_attn_b200.workloads import WORKLOADS, make_inputs, small
+
+    fta.set_kernel(kernel)
+    w = WORKLOADS[cfg]
+    if cfg == "cfg4":
+        w = small(w, ctx=32768)
+    w = small(w, B=B)
+    inp = make_inputs(w, "cuda")
+    out, lse = _run(fta, inp, w.G, ctx=w.ctx)
+    _check(out, lse, _oracle(inp, w.G), cfg)
+
+
+def test_kv_range_shards_merge_to_whole(fta):
+    """One sequence cut into KV ranges (what each GPU of a sequence-split job computes),
+    tree attached to the last range, merged by fta_merge_parts."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    w = _workload(B=1, H=16, G=8, D=128, Q=64, ctx=4096, lens="fixed:4096", dtype=torch.bfloat16)
+    inp = make_inputs(w, "cuda")
+    ora = _oracle(inp, 8)
+    n = 4
+    parts_o, parts_l = [], []
+    for r in range(n):
+        lo, hi = r * 1024, (r + 1) * 1024
+        sh = dict(inp)
+        sh["k_cache"], sh["v_cache"] = inp["k_cache"][:, :, lo:hi], inp["v_cache"][:, :, lo:hi]
+        sh["kv_seq_len"] = torch.tensor([1024], dtype=torch.int32, device="cuda")
+        o, l = _run(fta, sh, 8, out_dtype=torch.float32, with_tree=(r == n - 1))
+        parts_o.append(o)
+        parts_l.append(l)
+    out, lse = fta.merge_partials(torch.stack(parts_o), torch.stack(parts_l), torch.bfloat16)
+    _check(out, lse, ora, "kv-range shards")
