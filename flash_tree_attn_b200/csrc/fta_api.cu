@@ -132,7 +132,7 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
   g.U = p.Hkv * g.mtiles;
   g.n_tree = p.with_tree ? fta_cdiv(p.Q, FTA_TILE) : 0;
   g.min_per = 2;
-  g.fixed_max_splits = p.split_mode == FTA_SPLIT_FIXED ? fta_cdiv(p.ctx, p.split_tokens) : 0;
+  g.fixed_max_splits = (p.split_mode == FTA_SPLIT_FIXED && p.split_tokens > 0) ? fta_cdiv(p.ctx, p.split_tokens) : 0;
   g.pad_ = fam;
   g.grid = p.grid_override > 0 ? p.grid_override : 1;
   if (!need_grid || p.grid_override > 0) return FTA_OK;
@@ -154,7 +154,8 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
 }
 
 int64_t ws_bytes(const FtaParams& p, const FtaGeom& g) {
-  return (int64_t)2 * g.grid * g.R * (p.D + 1) * 4;
+  // partial O + partial LSE for two slots per block, then one int2 per unit
+  return (int64_t)2 * g.grid * g.R * (p.D + 1) * 4 + (int64_t)p.B * g.U * 8;
 }
 
 int run_stage1(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {

@@ -1,9 +1,566 @@
-// Stage 1, tcgen05 family (placeholder until the TMEM kernel lands): reports itself
-// unavailable so that every request runs on the warp-MMA family.
+// Stage 1, tcgen05 family: split-KV tree attention with both products on the 5th-generation
+// tensor cores.  One thread block owns one M tile of 128 rows (all tree queries x the GQA
+// heads that share a KV head) and streams 64-row KV tiles:
+//
+//   warp 0      TMA producer: Q once per piece of work, then K and V tiles (two 64-column
+//               boxes each, 128-byte swizzle) into a 4-stage ring guarded by mbarriers
+//   warp 1      MMA issuer: S = Q K^T (128x64, fp32 in TMEM, double-buffered) and
+//               O += P V (128x128, fp32 in TMEM); completion is signalled by tcgen05.commit
+//   warps 2..5  softmax: each thread owns one row (TMEM lane): tcgen05.ld of S, scale, tree
+//               mask / sequence-end mask, running max with lazy rescale of O, exp2, P (16-bit)
+//               written to shared memory in the swizzled K-major layout the MMA reads, and
+//               at the end of a piece the normalised O row and its LSE
+//
+// It replaces the reference's _flash_decoding_fwd_kernel (flash_tree_attn.py:14-144) and the
+// eager tree tail (flash_tree_attn.py:367-371) for head_dim 128 when M = G*Q is large enough
+// to fill a 128-row tile usefully; the work plan, the partial-result slots and the epilogue
+// are those of the warp-MMA family.
+//
+// Every mbarrier wait is bounded (fta_umma_ptx.cuh); on a timeout the block records a code in
+// g_umma_status, all roles leave their loops, and the block still frees its TMEM.
+#include <mutex>
+
 #include "fta_common.cuh"
+#include "fta_umma_ptx.cuh"
 
-int fta_umma_supported(const FtaParams&) { return 0; }
+namespace fta_umma {
 
-cudaError_t fta_launch_stage1_umma(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*) {
-  return cudaErrorNotSupported;
+constexpr int kThreads = 192;
+constexpr int NS = 4;  // K/V ring stages
+constexpr int kD = 128;
+constexpr int kR = 128;
+constexpr uint32_t kQHalf = kR * 128;         // 128 rows x 64 elements
+constexpr uint32_t kQBytes = 2 * kQHalf;
+constexpr uint32_t kKVHalf = FTA_TILE * 128;  // 64 rows x 64 elements
+constexpr uint32_t kKBytes = 2 * kKVHalf;
+constexpr uint32_t kStage = 2 * kKBytes;      // K tile then V tile
+constexpr uint32_t kPBytes = kR * 128;        // 128 rows x 64 KV columns, 16-bit
+constexpr uint32_t OFF_Q = 0;
+constexpr uint32_t OFF_RING = OFF_Q + kQBytes;
+constexpr uint32_t OFF_P = OFF_RING + NS * kStage;
+constexpr uint32_t OFF_BAR = OFF_P + 2 * kPBytes;
+constexpr uint32_t OFF_PRE = OFF_BAR + 256;
+constexpr uint32_t kTmemCols = 256;  // O: 0..127, S buffers: 128..191, 192..255
+constexpr uint32_t kColS = 128;
+
+// mbarrier slots
+enum { B_QFULL = 0, B_QEMPTY, B_ODONE, B_OFREE, B_KFULL, B_VFULL = B_KFULL + NS, B_KVEMPTY = B_VFULL + NS,
+       B_SFULL = B_KVEMPTY + NS, B_PREADY = B_SFULL + 2, B_FINAL = B_PREADY + 2, B_COUNT };
+static_assert(B_COUNT * 8 <= 192, "barrier area");
+
+struct Maps {
+  CUtensorMap q, k, v, ck, cv;
+};
+
+// Walks this block's pieces of work, identically in every role.
+struct Walker {
+  const FtaParams& p;
+  const FtaGeom& g;
+  FtaBalanced plan;
+  long long lin, lin_end, item, n_items;
+  __device__ Walker(const FtaParams& p_, const FtaGeom& g_, const int* pre) : p(p_), g(g_) {
+    lin = lin_end = item = n_items = 0;
+    if (p.split_mode == FTA_SPLIT_BALANCED) {
+      plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree;
+      plan.total = (long long)g.U * pre[p.B];
+      plan.per = FtaBalanced::choose_per(plan.total, gridDim.x, g.min_per);
+      lin = (long long)blockIdx.x * plan.per;
+      lin_end = lin + plan.per < plan.total ? lin + plan.per : plan.total;
+    } else {
+      item = blockIdx.x;
+      n_items = (long long)p.B * g.U * (g.fixed_max_splits + 1);
+    }
+  }
+  __device__ bool next(FtaSeg& seg) {
+    if (p.split_mode == FTA_SPLIT_BALANCED) {
+      if (lin >= lin_end) return false;
+      lin = plan.segment_at(blockIdx.x, lin, seg);
+      const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, seg.b, p.ctx);
+      if (seg.c1 > Lb) seg.c1 = Lb;
+      return true;
+    }
+    const int per_unit = g.fixed_max_splits + 1;
+    const long long per_b = (long long)g.U * per_unit;
+    while (item < n_items) {
+      seg.b = (int)(item / per_b);
+      const long long r = item - (long long)seg.b * per_b;
+      seg.j = (int)(r / per_unit);
+      seg.split = (int)(r - (long long)seg.j * per_unit);
+      item += gridDim.x;
+      seg.nsplit = 0; seg.slot = 0;
+      const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, seg.b, p.ctx);
+      if (seg.split == g.fixed_max_splits) {
+        if (g.n_tree == 0) continue;
+        seg.c0 = seg.c1 = 0; seg.tt0 = 0; seg.tt1 = g.n_tree;
+        return true;
+      }
+      seg.c0 = seg.split * p.split_tokens;
+      if (seg.c0 >= Lb) continue;
+      seg.c1 = seg.c0 + p.split_tokens < Lb ? seg.c0 + p.split_tokens : Lb;
+      seg.tt0 = seg.tt1 = 0;
+      return true;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ int seg_cache_tiles(const FtaSeg& s) {
+  return s.c1 > s.c0 ? fta_cdiv(s.c1 - s.c0, FTA_TILE) : 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ Maps maps) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzle atoms are 1024-byte aligned
+  uint8_t* sm = smem_raw + (base - raw);
+  int* pre = reinterpret_cast<int*>(sm + OFF_PRE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + 196);
+  const uint32_t bar0 = base + OFF_BAR;
+#define BAR(i) (bar0 + 8u * (uint32_t)(i))
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.H / p.Hkv;
+  const int fmt = sizeof(T) == 2 && p.dtype == FTA_DTYPE_BF16 ? 1 : 0;
+
+  if (tid == 0) {
+    mbar_init(BAR(B_QFULL), 1);
+    mbar_init(BAR(B_QEMPTY), 1);
+    mbar_init(BAR(B_ODONE), 1);
+    mbar_init(BAR(B_OFREE), 128);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR(B_KFULL + s), 1);
+      mbar_init(BAR(B_VFULL + s), 1);
+      mbar_init(BAR(B_KVEMPTY + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(B_SFULL + s), 1);
+      mbar_init(BAR(B_PREADY + s), 128);
+    }
+    mbar_init(BAR(B_FINAL), 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  // Q rows the TMA box never covers (M tile padding) must read as zero
+  for (uint32_t i = tid; i < kQBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sm + OFF_Q)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async();
+  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, pre);
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
+      if (g.n_tree) { tma_prefetch_desc(&maps.ck); tma_prefetch_desc(&maps.cv); }
+      Walker w(p, g, pre);
+      FtaSeg seg;
+      uint32_t gt = 0, sidx = 0;
+      bool ok = true;
+      while (ok && w.next(seg)) {
+        const FtaUnit unit = fta_unit(g, seg.j);
+        const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
+        ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
+        if (!ok) break;
+        mbar_expect_tx(BAR(B_QFULL), 2u * (uint32_t)(g.qpt * g.hpt) * 128u);
+        const int h0 = unit.kvh * G + unit.gt * g.hpt, q0 = unit.qt * g.qpt;
+        tma_load_4d(base + OFF_Q, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
+        tma_load_4d(base + OFF_Q + kQHalf, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
+        for (int i = 0; i < n; ++i, ++gt) {
+          const uint32_t st = gt % NS;
+          ok = mbar_wait(BAR(B_KVEMPTY + st), ((gt / NS) & 1) ^ 1, abort_flag, 0x102);
+          if (!ok) break;
+          const uint32_t sK = base + OFF_RING + st * kStage, sV = sK + kKBytes;
+          const CUtensorMap *mk, *mv;
+          int row0, head;
+          if (i < n_ct) { mk = &maps.k; mv = &maps.v; row0 = seg.c0 + i * FTA_TILE; head = unit.kvh; }
+          else { mk = &maps.ck; mv = &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = unit.kvh * p.cur_head_mul; }
+          mbar_expect_tx(BAR(B_KFULL + st), kKBytes);
+          tma_load_4d(sK, mk, BAR(B_KFULL + st), 0, row0, head, seg.b);
+          tma_load_4d(sK + kKVHalf, mk, BAR(B_KFULL + st), 64, row0, head, seg.b);
+          mbar_expect_tx(BAR(B_VFULL + st), kKBytes);
+          tma_load_4d(sV, mv, BAR(B_VFULL + st), 0, row0, head, seg.b);
+          tma_load_4d(sV + kKVHalf, mv, BAR(B_VFULL + st), 64, row0, head, seg.b);
+        }
+        ++sidx;
+      }
+    }
+  } else if (warp == 1) {
+    // ================================ MMA issuer ==================================
+    if (lane == 0) {
+      const uint32_t idesc_qk = instr_desc_f16(fmt, kR, FTA_TILE, 0, 0);
+      const uint32_t idesc_pv = instr_desc_f16(fmt, kR, kD, 0, 1);
+      auto issue_qk = [&](uint32_t st, uint32_t sbuf) {
+        const uint32_t sK = base + OFF_RING + st * kStage;
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+          umma_f16(tmem + kColS + FTA_TILE * sbuf,
+                   smem_desc_sw128(base + OFF_Q + half * kQHalf + off, 0, 1024),
+                   smem_desc_sw128(sK + half * kKVHalf + off, 0, 1024), idesc_qk, ks > 0);
+        }
+      };
+      auto issue_pv = [&](uint32_t st, uint32_t sbuf, bool accumulate) {
+        const uint32_t sV = base + OFF_RING + st * kStage + kKBytes;
+        const uint32_t sP = base + OFF_P + sbuf * kPBytes;
+#pragma unroll
+        for (int kk = 0; kk < FTA_TILE / 16; ++kk) {
+          umma_f16(tmem, smem_desc_sw128(sP + kk * 32, 0, 1024),
+                   smem_desc_sw128(sV + kk * 16 * 128, kKVHalf, 1024), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+      Walker w(p, g, pre);
+      FtaSeg seg;
+      uint32_t gt = 0, sidx = 0;
+      bool ok = true;
+      while (ok && w.next(seg)) {
+        const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
+        ok = mbar_wait(BAR(B_QFULL), sidx & 1, abort_flag, 0x201);
+        if (!ok) break;
+        ok = mbar_wait(BAR(B_KFULL + gt % NS), (gt / NS) & 1, abort_flag, 0x202);
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(gt % NS, gt & 1);
+        umma_commit(BAR(B_SFULL + (gt & 1)));
+        for (int i = 0; i < n; ++i) {
+          const uint32_t t = gt + i;
+          if (i + 1 < n) {
+            const uint32_t t1 = t + 1;
+            ok = mbar_wait(BAR(B_KFULL + t1 % NS), (t1 / NS) & 1, abort_flag, 0x203);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t1 % NS, t1 & 1);
+            umma_commit(BAR(B_SFULL + (t1 & 1)));
+          }
+          ok = mbar_wait(BAR(B_PREADY + (t & 1)), (t >> 1) & 1, abort_flag, 0x204);
+          if (!ok) break;
+          ok = mbar_wait(BAR(B_VFULL + t % NS), (t / NS) & 1, abort_flag, 0x205);
+          if (!ok) break;
+          if (i == 0) {  // the previous piece's epilogue must have read O
+            ok = mbar_wait(BAR(B_OFREE), (sidx & 1) ^ 1, abort_flag, 0x206);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          issue_pv(t % NS, t & 1, i > 0);
+          umma_commit(BAR(B_KVEMPTY + t % NS));
+          umma_commit(BAR(B_ODONE));
+        }
+        if (!ok) break;
+        umma_commit(BAR(B_QEMPTY));
+        gt += n;
+        ++sidx;
+      }
+      // nothing may still be running on the tensor pipe when TMEM is freed
+      umma_commit(BAR(B_FINAL));
+      int zero = 0;
+      mbar_wait(BAR(B_FINAL), 0, &zero, 0x2ff);
+    }
+  } else {
+    // ================================ softmax / epilogue ===========================
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+    const float scale2 = p.sm_scale * FTA_LOG2E;
+    float* ws_o = reinterpret_cast<float*>(p.workspace);
+    float* ws_l = ws_o + (long long)2 * g.grid * g.R * kD;
+    Walker w(p, g, pre);
+    FtaSeg seg;
+    uint32_t gt = 0;
+    bool ok = true;
+    while (ok && w.next(seg)) {
+      const FtaUnit unit = fta_unit(g, seg.j);
+      const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
+      int h, qi;
+      const bool rvalid = fta_row(p, g, unit, row, h, qi);
+      const float* mrow = (rvalid && g.n_tree) ? p.mask + seg.b * p.m_sb + h * p.m_sh + qi * p.m_sq : nullptr;
+      float m_used = -INFINITY, l = 0.f;
+      for (int i = 0; i < n; ++i) {
+        const uint32_t t = gt + i, sbuf = t & 1, st = t % NS;
+        ok = mbar_wait(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x301);
+        if (!ok) break;
+        tc_fence_after();
+        float s[FTA_TILE];
+        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf, s);
+        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + 32, s + 32);
+        tmem_ld_wait();
+
+        const bool is_tree = i >= n_ct;
+        int valid, col0 = 0;
+        if (!is_tree) {
+          const int row0 = seg.c0 + i * FTA_TILE;
+          valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
+        } else {
+          col0 = (seg.tt0 + i - n_ct) * FTA_TILE;
+          valid = p.Q - col0 < FTA_TILE ? p.Q - col0 : FTA_TILE;
+        }
+        float mt = -INFINITY;
+        if (is_tree && mrow != nullptr) {
+#pragma unroll
+          for (int c = 0; c < FTA_TILE; ++c) {
+            float v = s[c] * scale2;
+            if (c < valid) v += __ldg(mrow + col0 + c) * FTA_LOG2E;
+            else v = -INFINITY;
+            s[c] = v;
+            mt = fmaxf(mt, v);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < FTA_TILE; ++c) {
+            const float v = c < valid ? s[c] * scale2 : -INFINITY;
+            s[c] = v;
+            mt = fmaxf(mt, v);
+          }
+        }
+        // O and the P buffer two tiles back are only touched once the previous PV has finished
+        if (i > 0) {
+          ok = mbar_wait(BAR(B_ODONE), (t - 1) & 1, abort_flag, 0x302);
+          if (!ok) break;
+        }
+        // lazy rescale: keep the running max until it is exceeded by more than 2^8
+        const bool need = mt > m_used + 8.f;
+        if (i > 0 && __any_sync(0xffffffffu, need)) {
+          tc_fence_after();
+          const float alpha = need ? fta_exp2(m_used - mt) : 1.f;
+#pragma unroll
+          for (int ch = 0; ch < kD / 32; ++ch) {
+            float o[32];
+            tmem_ld32(t_lane + ch * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] *= alpha;
+            tmem_st32(t_lane + ch * 32, o);
+          }
+          tmem_st_wait();
+        }
+        if (need) {
+          l *= fta_exp2(m_used - mt);
+          m_used = mt;
+        }
+        const float msub = m_used == -INFINITY ? 0.f : m_used;
+        float psum = 0.f;
+        uint8_t* prow = sm + OFF_P + sbuf * kPBytes + row * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < FTA_TILE / 8; ++c8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float p0 = fta_exp2(s[c8 * 8 + 2 * k] - msub), p1 = fta_exp2(s[c8 * 8 + 2 * k + 1] - msub);
+            psum += p0 + p1;
+            pk[k] = FtaType<T>::pack(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        l += psum;
+        // V rows past the end of the sequence: zero them so that 0 * padding cannot give NaN
+        if (!is_tree && valid < FTA_TILE) {
+          ok = mbar_wait(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x303);
+          if (!ok) break;
+          uint8_t* sV = sm + OFF_RING + st * kStage + kKBytes;
+          const int nz = (FTA_TILE - valid) * 16;
+          for (int idx = tid - 64; idx < nz; idx += 128) {
+            const int rr = valid + (idx >> 4), hc = idx & 15;
+            *reinterpret_cast<uint4*>(sV + (hc >> 3) * kKVHalf + rr * 128 + (hc & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(BAR(B_PREADY + sbuf));
+      }
+      if (!ok) break;
+
+      // ---- epilogue of the piece: O row / l, LSE ------------------------------------------
+      const uint32_t t_last = gt + n - 1;
+      ok = mbar_wait(BAR(B_ODONE), t_last & 1, abort_flag, 0x304);
+      if (!ok) break;
+      tc_fence_after();
+      float o[kD];
+#pragma unroll
+      for (int ch = 0; ch < kD / 32; ++ch) tmem_ld32(t_lane + ch * 32, o + ch * 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(BAR(B_OFREE));
+
+      if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 0 && row == 0) {
+        int2* udesc = reinterpret_cast<int2*>(ws_l + (long long)2 * g.grid * g.R);
+        udesc[(long long)seg.b * g.U + seg.j] = make_int2(seg.nsplit, (seg.slot >> 1) | ((seg.slot & 1) << 31));
+      }
+      if (rvalid) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
+        const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
+        const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
+        void* dst;
+        int dt = FTA_DTYPE_F32;
+        long long off;
+        if (final_direct) {
+          dst = p.out; dt = p.out_dtype; off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
+          if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
+        } else if (p.split_mode == FTA_SPLIT_BALANCED) {
+          dst = ws_o; off = ((long long)seg.slot * g.R + row) * kD;
+          ws_l[(long long)seg.slot * g.R + row] = lse;
+        } else if (tree_piece) {
+          const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
+          dst = p.tree_o; off = ro * kD;
+          p.tree_lse[ro] = lse;
+        } else {
+          dst = p.mid_o; off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
+          p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < kD; c4 += 4)
+          fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
+      }
+      gt += n;
+    }
+  }
+
+  // ---- teardown -------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+#undef BAR
+}
+
+// ---- host side: tensor maps --------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int dtype;
+  uint64_t dims[4];
+  int64_t strides[3];
+  uint32_t box[4];
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kMapCache = 64;
+MapEntry g_maps[kMapCache];
+int g_map_next = 0;
+std::mutex g_map_mu;
+
+// 4-D map over a [B, heads, rows, 128] tensor with element strides (rows, heads, batch);
+// box = 64 columns x box_rows x box_heads x 1, 128-byte swizzle, zero fill out of bounds.
+bool make_map(CUtensorMap* out, const void* ptr, int dtype, uint64_t rows, uint64_t heads, uint64_t B, int64_t s_row,
+              int64_t s_head, int64_t s_batch, uint32_t box_rows, uint32_t box_heads) {
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.ptr = ptr; key.dtype = dtype;
+  key.dims[0] = kD; key.dims[1] = rows; key.dims[2] = heads; key.dims[3] = B;
+  // a stride of a size-1 dimension is never used; give it a value the encoder accepts
+  if (heads == 1) s_head = s_row * (int64_t)rows;
+  if (B == 1) s_batch = s_head * (int64_t)heads;
+  if (rows == 1) s_row = kD;
+  key.strides[0] = s_row; key.strides[1] = s_head; key.strides[2] = s_batch;
+  key.box[0] = 64; key.box[1] = box_rows; key.box[2] = box_heads; key.box[3] = 1;
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  for (int i = 0; i < kMapCache; ++i)
+    if (g_maps[i].used && g_maps[i].key == key) { *out = g_maps[i].map; return true; }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t gdim[4] = {key.dims[0], key.dims[1], key.dims[2], key.dims[3]};
+  cuuint64_t gstr[3] = {(cuuint64_t)s_row * 2, (cuuint64_t)s_head * 2, (cuuint64_t)s_batch * 2};
+  cuuint32_t box[4] = {key.box[0], key.box[1], key.box[2], key.box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMap m;
+  CUresult r = enc(&m, dtype == FTA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  MapEntry& e = g_maps[g_map_next];
+  g_map_next = (g_map_next + 1) % kMapCache;
+  e.key = key; e.map = m; e.used = true;
+  *out = m;
+  return true;
+}
+
+bool stride_ok(int64_t s) { return s > 0 && s % 8 == 0 && s * 2 < (1ll << 40); }
+
+}  // namespace fta_umma
+
+using namespace fta_umma;
+
+// The tcgen05 family serves head_dim 128 with positive 16-byte-multiple strides.
+int fta_umma_supported(const FtaParams& p) {
+  if (p.D != kD || p.ctx < 1 || p.B < 1) return 0;
+  if (!stride_ok(p.q_sq) || !stride_ok(p.k_st) || !stride_ok(p.v_st)) return 0;
+  if (p.H > 1 && !stride_ok(p.q_sh)) return 0;
+  if (p.Hkv > 1 && (!stride_ok(p.k_sh) || !stride_ok(p.v_sh))) return 0;
+  if (p.B > 1 && (!stride_ok(p.q_sb) || !stride_ok(p.k_sb) || !stride_ok(p.v_sb))) return 0;
+  if (p.with_tree) {
+    if (!stride_ok(p.ck_st) || !stride_ok(p.cv_st)) return 0;
+    if (p.Hkv * p.cur_head_mul > 1 && (!stride_ok(p.ck_sh) || !stride_ok(p.cv_sh))) return 0;
+    if (p.B > 1 && (!stride_ok(p.ck_sb) || !stride_ok(p.cv_sb))) return 0;
+  }
+  return get_encode() != nullptr ? 1 : 0;
+}
+
+cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStream_t st, int query_only,
+                                   int* blocks_per_sm) {
+  auto kern = p.dtype == FTA_DTYPE_F16 ? stage1_umma_kernel<__half> : stage1_umma_kernel<__nv_bfloat16>;
+  const size_t smem = (size_t)OFF_PRE + (size_t)(p.B + 1) * sizeof(int) + 1024;
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  static unsigned long long configured[2] = {0ull, 0ull};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const int ti = p.dtype == FTA_DTYPE_F16 ? 0 : 1;
+  if (!((configured[ti] >> (dev & 63)) & 1ull)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured[ti] |= 1ull << (dev & 63);
+  }
+  if (query_only) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, kern, kThreads, smem);
+
+  Maps maps;
+  const int Hcur = p.Hkv * p.cur_head_mul;
+  bool ok = make_map(&maps.q, p.q, p.dtype, p.Q, p.H, p.B, p.q_sq, p.q_sh, p.q_sb, g.qpt, g.hpt) &&
+            make_map(&maps.k, p.k_cache, p.dtype, p.ctx, p.Hkv, p.B, p.k_st, p.k_sh, p.k_sb, FTA_TILE, 1) &&
+            make_map(&maps.v, p.v_cache, p.dtype, p.ctx, p.Hkv, p.B, p.v_st, p.v_sh, p.v_sb, FTA_TILE, 1);
+  if (ok && p.with_tree) {
+    ok = make_map(&maps.ck, p.cur_k, p.dtype, p.Q, Hcur, p.B, p.ck_st, p.ck_sh, p.ck_sb, FTA_TILE, 1) &&
+         make_map(&maps.cv, p.cur_v, p.dtype, p.Q, Hcur, p.B, p.cv_st, p.cv_sh, p.cv_sb, FTA_TILE, 1);
+  } else if (ok) {
+    maps.ck = maps.k;
+    maps.cv = maps.v;
+  }
+  if (!ok) return cudaErrorInvalidValue;
+  kern<<<g.grid, kThreads, smem, st>>>(p, g, maps);
+  return cudaGetLastError();
+}
+
+// Reads and clears the device status word: 0, or the code of the first bounded wait that gave up.
+extern "C" int fta_umma_status(void) {
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_umma_status, sizeof(v)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(zero));
+  return (int)v;
 }

@@ -1,5 +1,5 @@
-// Stage 2: log-sum-exp merge of the partial attentions stage 1 left behind, one thread
-// block per unit (sequence, KV head, M tile), float4 along head_dim.
+// Stage 2: log-sum-exp merge of the partial attentions stage 1 left behind, one warp
+// per query row, float4 along head_dim.
 //
 // It replaces the reference's _flash_decoding_fwd_reduce_kernel (flash_tree_attn.py:146-211)
 // and the final two-way blend with the tree part (flash_tree_attn.py:373).  The recurrence
@@ -31,36 +31,49 @@ struct Acc {
   __device__ __forceinline__ float lse() const { return l > 0.f ? m + __logf(l) : -INFINITY; }
 };
 
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
+constexpr int kRowsPerBlock = kThreads / 32;
 
+// One warp per query row, one float4 of head_dim per lane (two for head_dim 256); grid =
+// (units, row groups).  Loads of up to four partials are issued before any is folded in.
 __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, const FtaGeom g) {
-  extern __shared__ int pre[];
   const int b = blockIdx.x / g.U, j = blockIdx.x - b * g.U;
+  const int row = blockIdx.y * kRowsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int D = p.D;
+  if (row >= g.R) return;
   const FtaUnit unit = fta_unit(g, j);
-  const int D = p.D, D4 = D >> 2;
+  int h, qi;
+  if (!fta_row(p, g, unit, row, h, qi)) return;
 
   if (p.split_mode == FTA_SPLIT_BALANCED) {
-    fta_build_prefix(p, g.n_tree, pre);
-    __syncthreads();
-    FtaBalanced plan;
-    plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree;
-    plan.total = (long long)g.U * pre[p.B];
-    plan.per = FtaBalanced::choose_per(plan.total, g.grid, g.min_per);
-    int cfirst; long long ustart;
-    const int np = plan.unit_pieces(b, j, cfirst, ustart);
-    if (np == 1) return;  // stage 1 wrote the final rows itself
+    // stage 1 left {pieces, first block | first-slot flag} for every unit that has work
     const float* ws_o = reinterpret_cast<const float*>(p.workspace);
     const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
-    for (int i = threadIdx.x; i < g.R * D4; i += kThreads) {
-      const int row = i / D4, c4 = (i - row * D4) * 4;
-      int h, qi;
-      if (!fta_row(p, g, unit, row, h, qi)) continue;
+    const int2* udesc = reinterpret_cast<const int2*>(ws_l + (long long)2 * g.grid * g.R);
+    int np = 0, cfirst = 0, flag = 0;
+    const bool empty_unit = g.n_tree == 0 && fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx) == 0;
+    if (!empty_unit) {
+      const int2 d = udesc[(long long)b * g.U + j];
+      np = d.x; cfirst = d.y & 0x7fffffff; flag = (d.y >> 31) & 1;
+      if (np == 1) return;  // stage 1 wrote the final rows itself
+    }
+    for (int c4 = lane * 4; c4 < D; c4 += 128) {
       Acc acc; acc.init();
-      for (int s = 0; s < np; ++s) {
-        const long long slot = plan.piece_slot(cfirst, ustart, s);
-        const float lse = ws_l[slot * g.R + row];
-        const float4 o = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row) * D + c4);
-        acc.add(lse, o);
+      for (int s0 = 0; s0 < np; s0 += 4) {
+        float lse[4]; float4 o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int s = s0 + k;
+          lse[k] = -INFINITY; o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (s < np) {
+            const long long slot = 2ll * (cfirst + s) + (s == 0 ? flag : 0);
+            lse[k] = ws_l[slot * g.R + row];
+            o[k] = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row) * D + c4);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc.add(lse[k], o[k]);
       }
       fta_store4(p.out, p.out_dtype, b * p.o_sb + h * p.o_sh + qi * p.o_sq + c4, acc.value());
       if (c4 == 0 && p.lse) p.lse[b * p.l_sb + h * p.l_sh + qi] = acc.lse();
@@ -71,15 +84,24 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
   // FIXED: cache partials in mid_o/mid_lse, the tree partial in tree_o/tree_lse
   const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx);
   const int np = fta_cdiv(Lb, p.split_tokens);
-  for (int i = threadIdx.x; i < g.R * D4; i += kThreads) {
-    const int row = i / D4, c4 = (i - row * D4) * 4;
-    int h, qi;
-    if (!fta_row(p, g, unit, row, h, qi)) continue;
+  for (int c4 = lane * 4; c4 < D; c4 += 128) {
     Acc acc; acc.init();
     const float* mo = p.mid_o + b * p.mo_sb + h * p.mo_sh + qi * p.mo_sq + c4;
     const float* ml = p.mid_lse + b * p.ml_sb + h * p.ml_sh + qi;
-    for (int s = 0; s < np; ++s)
-      acc.add(ml[s * p.ml_ss], *reinterpret_cast<const float4*>(mo + s * p.mo_ss));
+    for (int s0 = 0; s0 < np; s0 += 4) {
+      float lse[4]; float4 o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int s = s0 + k;
+        lse[k] = -INFINITY; o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s < np) {
+          lse[k] = ml[s * p.ml_ss];
+          o[k] = *reinterpret_cast<const float4*>(mo + s * p.mo_ss);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc.add(lse[k], o[k]);
+    }
     if (p.out_cache)
       fta_store4(p.out_cache, p.dtype, b * p.oc_sb + h * p.oc_sh + qi * p.oc_sq + c4, acc.value());
     if (g.n_tree > 0) {
@@ -109,8 +131,8 @@ __global__ void __launch_bounds__(kThreads) merge_parts_kernel(const FtaMergePar
 }  // namespace
 
 cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
-  const size_t smem = p.split_mode == FTA_SPLIT_BALANCED ? (size_t)(p.B + 1) * sizeof(int) : 0;
-  stage2_kernel<<<p.B * g.U, kThreads, smem, st>>>(p, g);
+  const dim3 grid(p.B * g.U, (g.R + kRowsPerBlock - 1) / kRowsPerBlock);
+  stage2_kernel<<<grid, kThreads, 0, st>>>(p, g);
   return cudaGetLastError();
 }
 

@@ -228,14 +228,15 @@ def prepare(
         keep.append(ws)
     else:
         # one partial per split: the reference's buffer layout (flash_tree_attn.py:276-281)
-        p.split_mode = _lib.SPLIT_FIXED
         if block_mode:
             split = block_size
         else:
+            p.split_mode = _lib.SPLIT_BALANCED  # only sizes are read by fta_plan_grid
             grid = max(lib.fta_plan_grid(C.byref(p)), 1)
             units = B * Hkv * max(1, (G * Q + 127) // 128)
             split = max(256, -(-(units * max(ctx, 1)) // (grid * 4)))
             split = min(-(-split // 64) * 64, max(64, -(-ctx // 64) * 64))
+        p.split_mode = _lib.SPLIT_FIXED
         p.split_tokens = split
         S = max(1, -(-ctx // split))
         use_caller_mid = (

@@ -40,11 +40,17 @@ def _run(fta, inp, G, block_size=64, ctx=None, **kw):
 
 
 def _check(out, lse, ora, tag=""):
+    """2e-3 on the output, plus half a unit in the last place of the output dtype where a
+    value is large enough for its own rounding to exceed that (short sequences give |o| ~ 1,
+    and bf16 keeps 8 bits); 1e-3 on the LSE."""
     assert out.dtype in (torch.float16, torch.bfloat16, torch.float32)
-    eo = (out.float() - ora["out"]).abs().max().item()
+    ref = ora["out"]
+    half_ulp = {torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8, torch.float32: 0.0}[out.dtype]
+    excess = ((out.float() - ref).abs() - half_ulp * ref.abs()).max().item()
+    eo = (out.float() - ref).abs().max().item()
     el = (lse - ora["lse"]).abs().max().item()
     assert torch.isfinite(out.float()).all(), tag
-    assert eo <= OUT_TOL, f"{tag}: out max-abs {eo}"
+    assert excess <= OUT_TOL, f"{tag}: out max-abs {eo} (beyond output rounding: {excess})"
     assert el <= LSE_TOL, f"{tag}: lse max-abs {el}"
     return eo, el
 
