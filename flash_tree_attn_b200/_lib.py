@@ -76,6 +76,7 @@ SYMBOLS = {
     "fta_plan_host": (_i64, [C.POINTER(FtaParams), C.POINTER(_i64), C.POINTER(_i64), _i64,
                              C.POINTER(_i32), C.POINTER(_i32)]),
     "fta_plan_grid": (C.c_int, [C.POINTER(FtaParams)]),
+    "fta_umma_status": (C.c_int, []),
 }
 
 _lib = None

@@ -104,6 +104,12 @@ struct Walker {
   }
 };
 
+// Warp-collective wait: every lane gets the same answer, so the lanes of a softmax warp leave
+// their loops together (the TMEM loads that follow are warp-wide instructions).
+__device__ __forceinline__ bool wait_all(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code)) != 0;
+}
+
 __device__ __forceinline__ int seg_cache_tiles(const FtaSeg& s) {
   return s.c1 > s.c0 ? fta_cdiv(s.c1 - s.c0, FTA_TILE) : 0;
 }
@@ -201,8 +207,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         for (int ks = 0; ks < kD / 16; ++ks) {
           const uint32_t half = ks >> 2, off = (ks & 3) * 32;
           umma_f16(tmem + kColS + FTA_TILE * sbuf,
-                   smem_desc_sw128(base + OFF_Q + half * kQHalf + off, 0, 1024),
-                   smem_desc_sw128(sK + half * kKVHalf + off, 0, 1024), idesc_qk, ks > 0);
+                   smem_desc_sw128(base + OFF_Q + half * kQHalf + off, 16, 1024),
+                   smem_desc_sw128(sK + half * kKVHalf + off, 16, 1024), idesc_qk, ks > 0);
         }
       };
       auto issue_pv = [&](uint32_t st, uint32_t sbuf, bool accumulate) {
@@ -210,7 +216,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         const uint32_t sP = base + OFF_P + sbuf * kPBytes;
 #pragma unroll
         for (int kk = 0; kk < FTA_TILE / 16; ++kk) {
-          umma_f16(tmem, smem_desc_sw128(sP + kk * 32, 0, 1024),
+          umma_f16(tmem, smem_desc_sw128(sP + kk * 32, 16, 1024),
                    smem_desc_sw128(sV + kk * 16 * 128, kKVHalf, 1024), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
         }
       };
@@ -281,7 +287,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       float m_used = -INFINITY, l = 0.f;
       for (int i = 0; i < n; ++i) {
         const uint32_t t = gt + i, sbuf = t & 1, st = t % NS;
-        ok = mbar_wait(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x301);
+        ok = wait_all(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x301);
         if (!ok) break;
         tc_fence_after();
         float s[FTA_TILE];
@@ -318,7 +324,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         }
         // O and the P buffer two tiles back are only touched once the previous PV has finished
         if (i > 0) {
-          ok = mbar_wait(BAR(B_ODONE), (t - 1) & 1, abort_flag, 0x302);
+          ok = wait_all(BAR(B_ODONE), (t - 1) & 1, abort_flag, 0x302);
           if (!ok) break;
         }
         // lazy rescale: keep the running max until it is exceeded by more than 2^8
@@ -358,7 +364,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         l += psum;
         // V rows past the end of the sequence: zero them so that 0 * padding cannot give NaN
         if (!is_tree && valid < FTA_TILE) {
-          ok = mbar_wait(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x303);
+          ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x303);
           if (!ok) break;
           uint8_t* sV = sm + OFF_RING + st * kStage + kKBytes;
           const int nz = (FTA_TILE - valid) * 16;
@@ -375,7 +381,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 
       // ---- epilogue of the piece: O row / l, LSE ------------------------------------------
       const uint32_t t_last = gt + n - 1;
-      ok = mbar_wait(BAR(B_ODONE), t_last & 1, abort_flag, 0x304);
+      ok = wait_all(BAR(B_ODONE), t_last & 1, abort_flag, 0x304);
       if (!ok) break;
       tc_fence_after();
       float o[kD];

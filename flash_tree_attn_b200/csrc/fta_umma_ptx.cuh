@@ -34,7 +34,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // (a code in a device status word), raises the block-wide abort flag and returns false; all
 // other waiters see the flag and leave too, so a protocol error ends the kernel instead of
 // hanging the GPU.
-constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
+constexpr long long kWaitCycles = 1000000000ll;  // about half a second
 
 __device__ unsigned int g_umma_status = 0u;
 

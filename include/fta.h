@@ -190,6 +190,13 @@ int fta_merge_parts(const FtaMergeParams* p, void* stream);
 int64_t fta_plan_host(const FtaParams* p, const int64_t* kv_seq_len_host, int64_t* segs_out,
                       int64_t max_segs, int32_t* grid_out, int32_t* per_out);
 
+/*
+ * Reads and clears the status word of the tcgen05 stage-1 kernel: 0, or the code of the
+ * first bounded barrier wait that gave up (the kernel then returns instead of hanging).
+ * Synchronises the device.  No counterpart in the reference.
+ */
+int fta_umma_status(void);
+
 /* Number of stage-1 thread blocks a call with these sizes launches on the current device. */
 int fta_plan_grid(const FtaParams* p);
 

@@ -10,6 +10,7 @@ from conftest import GOLDEN, load_golden
 pytestmark = pytest.mark.gpu
 
 OUT_TOL = 2e-3
+KERNELS = ["mma", "auto"]  # "auto" takes the tcgen05 family wherever it applies
 LSE_TOL = 1e-3
 
 
@@ -34,9 +35,15 @@ def _oracle(inp, G, with_tree=True):
 
 
 def _run(fta, inp, G, block_size=64, ctx=None, **kw):
-    return fta.flash_decoding_attention_with_lse(
+    from flash_tree_attn_b200 import _lib
+
+    res = fta.flash_decoding_attention_with_lse(
         inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
         inp["kv_seq_len"], block_size, ctx, kv_group_num=G, **kw)
+    torch.cuda.synchronize()
+    # a bounded barrier wait that gave up inside the tcgen05 kernel shows here, not as a hang
+    assert _lib.load().fta_umma_status() == 0, "tcgen05 stage-1 kernel reported a barrier timeout"
+    return res
 
 
 def _check(out, lse, ora, tag=""):
@@ -64,7 +71,7 @@ def _workload(**kw):
     return Workload(**base)
 
 
-@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("name", GOLDEN)
 def test_golden_fixtures(fta, name, kernel):
     fta.set_kernel(kernel)
@@ -97,7 +104,7 @@ SHAPES = [
 ]
 
 
-@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_shapes_against_oracle(fta, shape, dtype, kernel):
@@ -111,7 +118,7 @@ def test_shapes_against_oracle(fta, shape, dtype, kernel):
     _check(out, lse, _oracle(inp, G), str(shape))
 
 
-@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("grid", [1, 3, 37, 148, 1000])
 def test_result_independent_of_split_count(fta, grid, kernel):
     from flash_tree_attn_b200.workloads import make_inputs
@@ -126,7 +133,7 @@ def test_result_independent_of_split_count(fta, grid, kernel):
     _check(out, lse, ora, f"grid={grid}")
 
 
-@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("kernel", KERNELS)
 def test_padding_rows_are_never_read(fta, kernel):
     """NaN in every cache row at or past kv_seq_len must not reach the result (the reference
     needs finite padding, flash_tree_attn.py:93-94)."""
@@ -207,7 +214,7 @@ def test_current_kv_with_all_query_heads(fta):
     _check(out, lse, ora, "expanded current kv")
 
 
-@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("kernel", KERNELS)
 def test_output_argument_receives_cache_only_attention(fta, kernel):
     """Like the reference, `output` ends up holding the cache-only attention and the
     returned tensor is a different one (flash_tree_attn.py:340-376)."""
@@ -270,7 +277,7 @@ def test_reference_assertions_are_kept(fta):
         fta.flash_decoding_attention(bad, *a[1:])  # head_dim outside {32,64,128,256}
 
 
-@pytest.mark.parametrize("kernel", ["mma", "auto"])
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("cfg,B", [("cfg2", 8), ("cfg3", 8), ("cfg4", 1), ("cfg5", 16)])
 def test_benchmark_shapes(fta, cfg, B, kernel):
     """The benchmark configurations at full per-sequence size (batch reduced where the
