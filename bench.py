@@ -159,12 +159,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default=None, choices=[None, "auto", "mma", "umma"])
+    ap.add_argument("--skip-e2e", action="store_true", help="device-timed region only (profiling runs)")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     from flash_tree_attn_b200.workloads import WORKLOADS, draw_lengths, flops, kv_bytes, make_inputs, small
 
     w = WORKLOADS[args.workload]
+    if args.batch > 0:
+        w = small(w, B=args.batch, name=f"{w.name}[B={args.batch}]")
     if args.impl == "reference":
         reference_arm(args, w)
         return
@@ -258,20 +262,22 @@ def main():
                                          stage["kv_seq_len"], w.block_size, w.ctx, kv_group_num=w.G)
         out_host.copy_(o, non_blocking=True)
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    x0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    x1.record()
-    barrier()
-    ms_e2e = x0.elapsed_time(x1)
+    ms_e2e = float("nan")
+    if not args.skip_e2e:
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        x0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        x1.record()
+        barrier()
+        ms_e2e = x0.elapsed_time(x1)
 
     cold = None
     cache_bytes = 2 * inp["k_cache"].numel() * inp["k_cache"].element_size()
-    if cache_bytes <= 8 << 30:
+    if cache_bytes <= 8 << 30 and not args.skip_e2e:
         cold_host = (inp["k_cache"].cpu().pin_memory(), inp["v_cache"].cpu().pin_memory())
         n_cold = max(2, min(args.steps, 10))
         e2e_step(cold_host)

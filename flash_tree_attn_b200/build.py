@@ -28,7 +28,9 @@ SOURCES = [
     "fta_stage1_mma_d256.cu",
 ]
 
-NVCC_FLAGS = [
+EXTRA = os.environ.get("FTA_EXTRA_NVCC_FLAGS", "").split()
+
+NVCC_FLAGS = EXTRA + [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",

@@ -69,16 +69,26 @@ __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uin
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Copy `nrows` rows of D elements (row i at g + i*stride) into a swizzled tile; rows at or
-// past `valid` are zero-filled without touching memory.
+// Copy FTA_TILE rows of D elements (row i at g + i*stride) into a swizzled tile; rows at or
+// past `valid` are zero-filled without touching memory.  Each thread owns one 16-byte column
+// chunk and walks down the rows, so its swizzled shared-memory offset is a constant plus a
+// multiple of the pass pitch.
 template <typename T, int D>
-__device__ __forceinline__ void load_rows(uint32_t sdst, const T* g, long long stride, int valid, int nrows) {
+__device__ __forceinline__ void load_rows(uint32_t sdst, const T* g, long long stride, int valid) {
   constexpr int CH = D / 8;
-  for (int i = threadIdx.x; i < nrows * CH; i += kThreads) {
-    const int row = i / CH, ch = i - row * CH;
+  constexpr int RPP = kThreads / CH;  // rows per pass
+  const int ch = threadIdx.x % CH, r0 = threadIdx.x / CH;
+  const T* src = g + (long long)r0 * stride + ch * 8;
+  const long long step = (long long)RPP * stride;
+  const uint32_t d0 = sdst + r0 * (D * 2);
+  const uint32_t sw_const = (uint32_t)swz<CH>(r0, ch) << 4;
+#pragma unroll
+  for (int k = 0; k < FTA_TILE / RPP; ++k) {
+    const int row = r0 + k * RPP;
     const bool ok = row < valid;
-    const T* src = ok ? (g + (long long)row * stride + ch * 8) : g;
-    cp_async16(sdst + row * (D * 2) + (swz<CH>(row, ch) << 4), src, ok ? 16 : 0);
+    const uint32_t sw = (RPP % 8 == 0 || CH < 8) ? sw_const : ((uint32_t)swz<CH>(row, ch) << 4);
+    cp_async16(d0 + k * RPP * (D * 2) + sw, ok ? src : g, ok ? 16 : 0);
+    src += step;
   }
 }
 
@@ -175,13 +185,13 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
         if (i < n_ct) {
           const int row0 = seg.c0 + i * FTA_TILE;
           const int valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
-          load_rows<T, D>(sK, kbase + (long long)row0 * p.k_st, p.k_st, valid, FTA_TILE);
-          load_rows<T, D>(sV, vbase + (long long)row0 * p.v_st, p.v_st, valid, FTA_TILE);
+          load_rows<T, D>(sK, kbase + (long long)row0 * p.k_st, p.k_st, valid);
+          load_rows<T, D>(sV, vbase + (long long)row0 * p.v_st, p.v_st, valid);
         } else {
           const int row0 = (seg.tt0 + i - n_ct) * FTA_TILE;
           const int valid = p.Q - row0 < FTA_TILE ? p.Q - row0 : FTA_TILE;
-          load_rows<T, D>(sK, ckbase + (long long)row0 * p.ck_st, p.ck_st, valid, FTA_TILE);
-          load_rows<T, D>(sV, cvbase + (long long)row0 * p.cv_st, p.cv_st, valid, FTA_TILE);
+          load_rows<T, D>(sK, ckbase + (long long)row0 * p.ck_st, p.ck_st, valid);
+          load_rows<T, D>(sV, cvbase + (long long)row0 * p.cv_st, p.cv_st, valid);
         }
       }
       cp_async_commit();

@@ -3,13 +3,18 @@
 // heads that share a KV head) and streams 64-row KV tiles:
 //
 //   warp 0      TMA producer: Q once per piece of work, then K and V tiles (two 64-column
-//               boxes each, 128-byte swizzle) into a 4-stage ring guarded by mbarriers
-//   warp 1      MMA issuer: S = Q K^T (128x64, fp32 in TMEM, double-buffered) and
-//               O += P V (128x128, fp32 in TMEM); completion is signalled by tcgen05.commit
-//   warps 2..5  softmax: each thread owns one row (TMEM lane): tcgen05.ld of S, scale, tree
-//               mask / sequence-end mask, running max with lazy rescale of O, exp2, P (16-bit)
-//               written to shared memory in the swizzled K-major layout the MMA reads, and
-//               at the end of a piece the normalised O row and its LSE
+//               boxes each, 128-byte swizzle) into a 5- or 6-stage ring guarded by mbarriers;
+//               K tiles are requested two tiles ahead of V tiles, as they are consumed
+//   warp 1      issuer of S = Q K^T (128x64, fp32 in TMEM, double-buffered, up to two tiles
+//               ahead of the softmax)
+//   warp 6      issuer of O += P V (128x128, fp32 in TMEM).  The A operands Q and P are read
+//               from TMEM, so only K and V cross shared memory; completion of either product is
+//               signalled by tcgen05.commit.  Two issuers because one thread cannot feed the
+//               tensor pipe with 12 small products per tile and answer five barriers in time
+//   warps 2..5  softmax: a thread owns one row (TMEM lane): copies its Q row into TMEM at the
+//               start of a piece; per tile tcgen05.ld of S, scale, tree mask / sequence-end
+//               mask, running max with lazy rescale of O, exp2, P (16-bit pairs) stored to
+//               TMEM; at the end of a piece the normalised O row and its LSE
 //
 // It replaces the reference's _flash_decoding_fwd_kernel (flash_tree_attn.py:14-144) and the
 // eager tree tail (flash_tree_attn.py:367-371) for head_dim 128 when M = G*Q is large enough
@@ -25,8 +30,7 @@
 
 namespace fta_umma {
 
-constexpr int kThreads = 192;
-constexpr int NS = 4;  // K/V ring stages
+constexpr int kThreads = 224;  // warp 0 TMA producer, 1 QK issuer, 2-5 softmax, 6 PV issuer
 constexpr int kD = 128;
 constexpr int kR = 128;
 constexpr uint32_t kQHalf = kR * 128;         // 128 rows x 64 elements
@@ -34,19 +38,28 @@ constexpr uint32_t kQBytes = 2 * kQHalf;
 constexpr uint32_t kKVHalf = FTA_TILE * 128;  // 64 rows x 64 elements
 constexpr uint32_t kKBytes = 2 * kKVHalf;
 constexpr uint32_t kStage = 2 * kKBytes;      // K tile then V tile
-constexpr uint32_t kPBytes = kR * 128;        // 128 rows x 64 KV columns, 16-bit
 constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_RING = OFF_Q + kQBytes;
-constexpr uint32_t OFF_P = OFF_RING + NS * kStage;
-constexpr uint32_t OFF_BAR = OFF_P + 2 * kPBytes;
-constexpr uint32_t OFF_PRE = OFF_BAR + 256;
-constexpr uint32_t kTmemCols = 256;  // O: 0..127, S buffers: 128..191, 192..255
-constexpr uint32_t kColS = 128;
+constexpr uint32_t kBarBytes = 448;
+// TMEM columns (32-bit): O fp32 | S fp32 x2 | Q 16-bit pairs | P 16-bit pairs x2
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 128;  // + 64 * buffer
+constexpr uint32_t kColQ = 256;  // 64 columns: 128 head-dim elements, two per column
+constexpr uint32_t kColP = 320;  // + 32 * buffer: 64 KV columns, two per column
+// shared-memory size of a block with NS ring stages and a B-entry prefix table
+constexpr size_t smem_bytes(int ns, int B) { return (size_t)OFF_RING + (size_t)ns * kStage + kBarBytes + (size_t)(B + 1) * 4 + 1024; }
 
-// mbarrier slots
-enum { B_QFULL = 0, B_QEMPTY, B_ODONE, B_OFREE, B_KFULL, B_VFULL = B_KFULL + NS, B_KVEMPTY = B_VFULL + NS,
-       B_SFULL = B_KVEMPTY + NS, B_PREADY = B_SFULL + 2, B_FINAL = B_PREADY + 2, B_COUNT };
-static_assert(B_COUNT * 8 <= 192, "barrier area");
+// mbarrier slots (ring barriers are sized for the largest ring)
+constexpr int kMaxNS = 6;
+enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
+       B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + 2,
+       B_FINAL = B_PREADY + 2, B_COUNT = B_FINAL + 2 };
+// A parity wait is only meaningful while the barrier is at most one phase ahead of the phase
+// asked for.  PV(t) therefore commits to B_ODONE + (t & 3): whoever has seen S(t') ready knows
+// that PV(t'-4) and everything before it is complete, so for t in [t'-3, t'] the barrier of PV(t)
+// has completed phase (t>>2)-1 and cannot have completed more than phase t>>2.
+constexpr uint32_t kBarArea = 448;
+static_assert(B_COUNT * 8 + 8 <= kBarArea, "barrier area");
 
 struct Maps {
   CUtensorMap q, k, v, ck, cv;
@@ -114,38 +127,48 @@ __device__ __forceinline__ int seg_cache_tiles(const FtaSeg& s) {
   return s.c1 > s.c0 ? fta_cdiv(s.c1 - s.c0, FTA_TILE) : 0;
 }
 
-template <typename T>
+template <typename T, int NS>
 __global__ void __launch_bounds__(kThreads, 1)
 stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ Maps maps) {
+  constexpr uint32_t OFF_BAR = OFF_RING + NS * kStage;
+  constexpr uint32_t OFF_PRE = OFF_BAR + kBarBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzle atoms are 1024-byte aligned
   uint8_t* sm = smem_raw + (base - raw);
   int* pre = reinterpret_cast<int*>(sm + OFF_PRE);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 192);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + 196);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 440);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + 444);
   const uint32_t bar0 = base + OFF_BAR;
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef FTA_UMMA_PROFILE
+  const long long prof_t0 = clock64();
+  unsigned long long prof_g0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
+#endif
   const int G = p.H / p.Hkv;
-  const int fmt = sizeof(T) == 2 && p.dtype == FTA_DTYPE_BF16 ? 1 : 0;
+  const int fmt = p.dtype == FTA_DTYPE_BF16 ? 1 : 0;
 
   if (tid == 0) {
     mbar_init(BAR(B_QFULL), 1);
-    mbar_init(BAR(B_QEMPTY), 1);
-    mbar_init(BAR(B_ODONE), 1);
+    mbar_init(BAR(B_QEMPTY), 128);
+    mbar_init(BAR(B_QREADY), 128);
+    for (int s = 0; s < 4; ++s) mbar_init(BAR(B_ODONE + s), 1);
     mbar_init(BAR(B_OFREE), 128);
     for (int s = 0; s < NS; ++s) {
       mbar_init(BAR(B_KFULL + s), 1);
       mbar_init(BAR(B_VFULL + s), 1);
-      mbar_init(BAR(B_KVEMPTY + s), 1);
+      mbar_init(BAR(B_KEMPTY + s), 1);
+      mbar_init(BAR(B_VEMPTY + s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(BAR(B_SFULL + s), 1);
       mbar_init(BAR(B_PREADY + s), 128);
     }
     mbar_init(BAR(B_FINAL), 1);
+    mbar_init(BAR(B_FINAL + 1), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -171,130 +194,215 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       while (ok && w.next(seg)) {
         const FtaUnit unit = fta_unit(g, seg.j);
         const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
-        ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
-        if (!ok) break;
-        mbar_expect_tx(BAR(B_QFULL), 2u * (uint32_t)(g.qpt * g.hpt) * 128u);
-        const int h0 = unit.kvh * G + unit.gt * g.hpt, q0 = unit.qt * g.qpt;
-        tma_load_4d(base + OFF_Q, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
-        tma_load_4d(base + OFF_Q + kQHalf, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
-        for (int i = 0; i < n; ++i, ++gt) {
-          const uint32_t st = gt % NS;
-          ok = mbar_wait(BAR(B_KVEMPTY + st), ((gt / NS) & 1) ^ 1, abort_flag, 0x102);
-          if (!ok) break;
-          const uint32_t sK = base + OFF_RING + st * kStage, sV = sK + kKBytes;
-          const CUtensorMap *mk, *mv;
-          int row0, head;
-          if (i < n_ct) { mk = &maps.k; mv = &maps.v; row0 = seg.c0 + i * FTA_TILE; head = unit.kvh; }
-          else { mk = &maps.ck; mv = &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = unit.kvh * p.cur_head_mul; }
-          mbar_expect_tx(BAR(B_KFULL + st), kKBytes);
-          tma_load_4d(sK, mk, BAR(B_KFULL + st), 0, row0, head, seg.b);
-          tma_load_4d(sK + kKVHalf, mk, BAR(B_KFULL + st), 64, row0, head, seg.b);
-          mbar_expect_tx(BAR(B_VFULL + st), kKBytes);
-          tma_load_4d(sV, mv, BAR(B_VFULL + st), 0, row0, head, seg.b);
-          tma_load_4d(sV + kKVHalf, mv, BAR(B_VFULL + st), 64, row0, head, seg.b);
+        const int q_at = n < 2 ? n : 2;
+        // K tiles run two ahead of V tiles, as their consumers (S = Q K^T, O += P V) do.  The
+        // first K tiles of a piece are requested before its Q tile: they do not depend on the
+        // Q buffer of the previous piece having been read, so they overlap its tail.
+        for (int u = 0; u < n + 2 && ok; ++u) {
+          if (u == q_at) {
+            ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
+            if (!ok) break;
+            mbar_expect_tx(BAR(B_QFULL), 2u * (uint32_t)(g.qpt * g.hpt) * 128u);
+            const int h0 = unit.kvh * G + unit.gt * g.hpt, q0 = unit.qt * g.qpt;
+            tma_load_4d(base + OFF_Q, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
+            tma_load_4d(base + OFF_Q + kQHalf, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
+          }
+          for (int which = 0; which < 2; ++which) {  // 0: K of tile u, 1: V of tile u - 2
+            const int i = which == 0 ? u : u - 2;
+            if (i < 0 || i >= n) continue;
+            const uint32_t t = gt + i, st = t % NS;
+            const CUtensorMap* m;
+            int row0, head;
+            if (i < n_ct) { m = which == 0 ? &maps.k : &maps.v; row0 = seg.c0 + i * FTA_TILE; head = unit.kvh; }
+            else { m = which == 0 ? &maps.ck : &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = unit.kvh * p.cur_head_mul; }
+            const uint32_t full = BAR((which == 0 ? B_KFULL : B_VFULL) + st);
+            ok = mbar_wait(BAR((which == 0 ? B_KEMPTY : B_VEMPTY) + st), ((t / NS) & 1) ^ 1, abort_flag, 0x102 + which);
+            if (!ok) break;
+            const uint32_t dst = base + OFF_RING + st * kStage + (which == 0 ? 0u : kKBytes);
+            mbar_expect_tx(full, kKBytes);
+            tma_load_4d(dst, m, full, 0, row0, head, seg.b);
+            tma_load_4d(dst + kKVHalf, m, full, 64, row0, head, seg.b);
+          }
         }
+        gt += n;
         ++sidx;
       }
     }
   } else if (warp == 1) {
-    // ================================ MMA issuer ==================================
-    if (lane == 0) {
-      const uint32_t idesc_qk = instr_desc_f16(fmt, kR, FTA_TILE, 0, 0);
-      const uint32_t idesc_pv = instr_desc_f16(fmt, kR, kD, 0, 1);
-      auto issue_qk = [&](uint32_t st, uint32_t sbuf) {
-        const uint32_t sK = base + OFF_RING + st * kStage;
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) {
-          const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-          umma_f16(tmem + kColS + FTA_TILE * sbuf,
-                   smem_desc_sw128(base + OFF_Q + half * kQHalf + off, 16, 1024),
-                   smem_desc_sw128(sK + half * kKVHalf + off, 16, 1024), idesc_qk, ks > 0);
+    // ================================ S = Q K^T issuer ============================
+    // The whole warp walks the loop (uniform control flow keeps descriptor arithmetic cheap);
+    // one elected lane issues.  S(t) goes to buffer t&1 as soon as the softmax has finished
+    // reading S(t-2), so the products run up to two tiles ahead of the softmax.
+    const uint32_t idesc_qk = instr_desc_f16(fmt, kR, FTA_TILE, 0, 0);
+    const uint64_t dK0 = smem_desc_sw128(base + OFF_RING, 16, 1024);
+    Walker w(p, g, pre);
+    FtaSeg seg;
+    uint32_t gt = 0, sidx = 0;
+    bool ok = true;
+    while (ok && w.next(seg)) {
+      const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
+      ok = wait_all(BAR(B_QREADY), sidx & 1, abort_flag, 0x201);  // Q rows are in TMEM
+      for (int i = 0; i < n && ok; ++i) {
+        const uint32_t t = gt + i, st = t % NS, sbuf = t & 1;
+        if (t >= 2) {
+          ok = wait_all(BAR(B_PREADY + sbuf), ((t - 2) >> 1) & 1, abort_flag, 0x204);
+          if (!ok) break;
         }
-      };
-      auto issue_pv = [&](uint32_t st, uint32_t sbuf, bool accumulate) {
-        const uint32_t sV = base + OFF_RING + st * kStage + kKBytes;
-        const uint32_t sP = base + OFF_P + sbuf * kPBytes;
-#pragma unroll
-        for (int kk = 0; kk < FTA_TILE / 16; ++kk) {
-          umma_f16(tmem, smem_desc_sw128(sP + kk * 32, 16, 1024),
-                   smem_desc_sw128(sV + kk * 16 * 128, kKVHalf, 1024), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
-        }
-      };
-      Walker w(p, g, pre);
-      FtaSeg seg;
-      uint32_t gt = 0, sidx = 0;
-      bool ok = true;
-      while (ok && w.next(seg)) {
-        const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
-        ok = mbar_wait(BAR(B_QFULL), sidx & 1, abort_flag, 0x201);
-        if (!ok) break;
-        ok = mbar_wait(BAR(B_KFULL + gt % NS), (gt / NS) & 1, abort_flag, 0x202);
+        ok = wait_all(BAR(B_KFULL + st), (t / NS) & 1, abort_flag, 0x202);
         if (!ok) break;
         tc_fence_after();
-        issue_qk(gt % NS, gt & 1);
-        umma_commit(BAR(B_SFULL + (gt & 1)));
-        for (int i = 0; i < n; ++i) {
-          const uint32_t t = gt + i;
-          if (i + 1 < n) {
-            const uint32_t t1 = t + 1;
-            ok = mbar_wait(BAR(B_KFULL + t1 % NS), (t1 / NS) & 1, abort_flag, 0x203);
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(t1 % NS, t1 & 1);
-            umma_commit(BAR(B_SFULL + (t1 & 1)));
+        if (elect_one()) {
+          const uint64_t dK = dK0 + (uint64_t)((st * kStage) >> 4);
+          const uint32_t d_tmem = tmem + kColS + FTA_TILE * sbuf;
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) {
+            const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+            umma_f16_ts(d_tmem, tmem + kColQ + ks * 8, dK + (uint64_t)((half * kKVHalf + off) >> 4), idesc_qk, ks > 0);
           }
-          ok = mbar_wait(BAR(B_PREADY + (t & 1)), (t >> 1) & 1, abort_flag, 0x204);
-          if (!ok) break;
-          ok = mbar_wait(BAR(B_VFULL + t % NS), (t / NS) & 1, abort_flag, 0x205);
-          if (!ok) break;
-          if (i == 0) {  // the previous piece's epilogue must have read O
-            ok = mbar_wait(BAR(B_OFREE), (sidx & 1) ^ 1, abort_flag, 0x206);
-            if (!ok) break;
-          }
-          tc_fence_after();
-          issue_pv(t % NS, t & 1, i > 0);
-          umma_commit(BAR(B_KVEMPTY + t % NS));
-          umma_commit(BAR(B_ODONE));
+          umma_commit(BAR(B_KEMPTY + st));
+          umma_commit(BAR(B_SFULL + sbuf));
         }
-        if (!ok) break;
-        umma_commit(BAR(B_QEMPTY));
-        gt += n;
-        ++sidx;
+        __syncwarp();
       }
-      // nothing may still be running on the tensor pipe when TMEM is freed
-      umma_commit(BAR(B_FINAL));
-      int zero = 0;
-      mbar_wait(BAR(B_FINAL), 0, &zero, 0x2ff);
+      gt += n;
+      ++sidx;
     }
-  } else {
+    // nothing of this warp's may still be running on the tensor pipe when TMEM is freed
+    if (elect_one()) umma_commit(BAR(B_FINAL));
+    __syncwarp();
+    int zero = 0;
+    mbar_wait(BAR(B_FINAL), 0, &zero, 0x20f);
+  } else if (warp == 6) {
+    // ================================ O += P V issuer =============================
+    const uint32_t idesc_pv = instr_desc_f16(fmt, kR, kD, 0, 1);
+    const uint64_t dV0 = smem_desc_sw128(base + OFF_RING + kKBytes, kKVHalf, 1024);
+    Walker w(p, g, pre);
+    FtaSeg seg;
+    uint32_t gt = 0, sidx = 0;
+    bool ok = true;
+    while (ok && w.next(seg)) {
+      const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
+      for (int i = 0; i < n && ok; ++i) {
+        const uint32_t t = gt + i, st = t % NS, sbuf = t & 1;
+        ok = wait_all(BAR(B_PREADY + sbuf), (t >> 1) & 1, abort_flag, 0x214);  // P(t) is in TMEM
+        if (!ok) break;
+        ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x215);
+        if (!ok) break;
+        if (i == 0) {  // the previous piece's epilogue must have read O
+          ok = wait_all(BAR(B_OFREE), (sidx & 1) ^ 1, abort_flag, 0x216);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        if (elect_one()) {
+          const uint64_t dV = dV0 + (uint64_t)((st * kStage) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < FTA_TILE / 16; ++kk)
+            umma_f16_ts(tmem, tmem + kColP + 32 * sbuf + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
+                        (i > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(BAR(B_VEMPTY + st));
+          umma_commit(BAR(B_ODONE + (t & 3)));
+        }
+        __syncwarp();
+      }
+      gt += n;
+      ++sidx;
+    }
+    if (elect_one()) umma_commit(BAR(B_FINAL + 1));
+    __syncwarp();
+    int zero = 0;
+    mbar_wait(BAR(B_FINAL + 1), 0, &zero, 0x21f);
+  } else if (warp >= 2 && warp < 6) {
     // ================================ softmax / epilogue ===========================
-    const int quad = warp & 3;
+    const int quad = warp & 3;  // the TMEM lane quadrant a warp may touch is fixed by its index
     const int row = quad * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
     const float scale2 = p.sm_scale * FTA_LOG2E;
     float* ws_o = reinterpret_cast<float*>(p.workspace);
     float* ws_l = ws_o + (long long)2 * g.grid * g.R * kD;
     Walker w(p, g, pre);
-    FtaSeg seg;
-    uint32_t gt = 0;
+    uint32_t gt = 0, sidx = 0;
     bool ok = true;
-    while (ok && w.next(seg)) {
+
+    // Q row of this thread: shared memory (TMA, swizzled) -> TMEM, 16-bit pairs, one per column.
+    // All MMAs of the previous piece are complete when this runs (its O has been read).
+    auto q_to_tmem = [&]() -> bool {
+      if (!wait_all(BAR(B_QFULL), sidx & 1, abort_flag, 0x306)) return false;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t qr[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sm + OFF_Q + hf * kQHalf + row * 128 + ((c ^ (row & 7)) << 4));
+          qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
+        }
+        tmem_st32(t_lane + kColQ + 32 * hf, reinterpret_cast<const float*>(qr));
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(BAR(B_QREADY));
+      mbar_arrive(BAR(B_QEMPTY));
+      ++sidx;
+      return true;
+    };
+    // V rows past the end of the sequence are zeroed so that 0 * padding cannot give NaN
+    auto zero_v_tail = [&](uint32_t t, int valid) -> bool {
+      const uint32_t st = t % NS;
+      if (!wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x303)) return false;
+      uint8_t* sV = sm + OFF_RING + st * kStage + kKBytes;
+      const int nz = (FTA_TILE - valid) * 16;
+      for (int idx = row; idx < nz; idx += 128) {
+        const int rr = valid + (idx >> 4), hc = idx & 15;
+        *reinterpret_cast<uint4*>(sV + (hc >> 3) * kKVHalf + rr * 128 + (hc & 7) * 16) = make_uint4(0, 0, 0, 0);
+      }
+      fence_proxy_async();
+      return true;
+    };
+
+    FtaSeg seg;
+    bool have = w.next(seg);
+    if (have) ok = q_to_tmem();
+    while (ok && have) {
       const FtaUnit unit = fta_unit(g, seg.j);
       const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
       int h, qi;
       const bool rvalid = fta_row(p, g, unit, row, h, qi);
       const float* mrow = (rvalid && g.n_tree) ? p.mask + seg.b * p.m_sb + h * p.m_sh + qi * p.m_sq : nullptr;
       float m_used = -INFINITY, l = 0.f;
+      const uint32_t t_last = gt + n - 1;
+      const bool working = __any_sync(0xffffffffu, rvalid) != 0;
+      FtaSeg nseg;
+      bool nhave;
+
+      if (!working) {
+        // a warp whose 32 rows are all M-tile padding only keeps the barrier protocol going
+        for (int i = 0; i < n; ++i) {
+          const uint32_t t = gt + i, sbuf = t & 1;
+          ok = wait_all(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x311);
+          if (!ok) break;
+          if (i < n_ct) {
+            const int row0 = seg.c0 + i * FTA_TILE;
+            const int valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
+            if (valid < FTA_TILE) {
+              ok = zero_v_tail(t, valid);
+              if (!ok) break;
+            }
+          }
+          mbar_arrive(BAR(B_PREADY + sbuf));
+        }
+        if (!ok) break;
+        ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x314);
+        if (!ok) break;
+        mbar_arrive(BAR(B_OFREE));
+        gt += n;
+        have = w.next(seg);
+        if (have) ok = q_to_tmem();
+        continue;
+      }
+
       for (int i = 0; i < n; ++i) {
-        const uint32_t t = gt + i, sbuf = t & 1, st = t % NS;
+        const uint32_t t = gt + i, sbuf = t & 1;
         ok = wait_all(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x301);
         if (!ok) break;
-        tc_fence_after();
-        float s[FTA_TILE];
-        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf, s);
-        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + 32, s + 32);
-        tmem_ld_wait();
-
         const bool is_tree = i >= n_ct;
         int valid, col0 = 0;
         if (!is_tree) {
@@ -304,32 +412,52 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           col0 = (seg.tt0 + i - n_ct) * FTA_TILE;
           valid = p.Q - col0 < FTA_TILE ? p.Q - col0 : FTA_TILE;
         }
-        float mt = -INFINITY;
-        if (is_tree && mrow != nullptr) {
+        tc_fence_after();
+        float s[FTA_TILE];
+        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf, s);
+        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + 32, s + 32);
+        tmem_ld_wait();
+
+        // Row maximum in the log2 domain (mt) and the factor `mul` that takes s[] there.
+        // Full cache tiles keep the raw scores and fold the scale into the exponent's FMA;
+        // the tree tile and the last, partial tile of a sequence take the general path.
+        float mt, mul;
+        if (!is_tree && valid == FTA_TILE && scale2 > 0.f) {
+          float mx[8];
 #pragma unroll
-          for (int c = 0; c < FTA_TILE; ++c) {
-            float v = s[c] * scale2;
-            if (c < valid) v += __ldg(mrow + col0 + c) * FTA_LOG2E;
-            else v = -INFINITY;
-            s[c] = v;
-            mt = fmaxf(mt, v);
-          }
+          for (int c = 0; c < 8; ++c) mx[c] = s[c];
+#pragma unroll
+          for (int c = 8; c < FTA_TILE; ++c) mx[c & 7] = fmaxf(mx[c & 7], s[c]);
+          mt = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
+          mul = scale2;
         } else {
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (is_tree && mrow != nullptr) {
 #pragma unroll
-          for (int c = 0; c < FTA_TILE; ++c) {
-            const float v = c < valid ? s[c] * scale2 : -INFINITY;
-            s[c] = v;
-            mt = fmaxf(mt, v);
+            for (int c = 0; c < FTA_TILE; ++c) {
+              float v = s[c] * scale2;
+              if (c < valid) v += __ldg(mrow + col0 + c) * FTA_LOG2E;
+              else v = -INFINITY;
+              s[c] = v;
+              mx[c & 3] = fmaxf(mx[c & 3], v);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < FTA_TILE; ++c) {
+              const float v = c < valid ? s[c] * scale2 : -INFINITY;
+              s[c] = v;
+              mx[c & 3] = fmaxf(mx[c & 3], v);
+            }
           }
+          mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+          mul = 1.f;
         }
-        // O and the P buffer two tiles back are only touched once the previous PV has finished
-        if (i > 0) {
-          ok = wait_all(BAR(B_ODONE), (t - 1) & 1, abort_flag, 0x302);
-          if (!ok) break;
-        }
-        // lazy rescale: keep the running max until it is exceeded by more than 2^8
+        // lazy rescale: keep the running max until it is exceeded by more than 2^8; O may only be
+        // touched once the previous PV has finished
         const bool need = mt > m_used + 8.f;
         if (i > 0 && __any_sync(0xffffffffu, need)) {
+          ok = wait_all(BAR(B_ODONE + ((t - 1) & 3)), ((t - 1) >> 2) & 1, abort_flag, 0x302);
+          if (!ok) break;
           tc_fence_after();
           const float alpha = need ? fta_exp2(m_used - mt) : 1.f;
 #pragma unroll
@@ -347,41 +475,34 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           l *= fta_exp2(m_used - mt);
           m_used = mt;
         }
-        const float msub = m_used == -INFINITY ? 0.f : m_used;
-        float psum = 0.f;
-        uint8_t* prow = sm + OFF_P + sbuf * kPBytes + row * 128;
+        const float nsub = m_used == -INFINITY ? 0.f : -m_used;
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[FTA_TILE / 2];
 #pragma unroll
-        for (int c8 = 0; c8 < FTA_TILE / 8; ++c8) {
-          uint32_t pk[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float p0 = fta_exp2(s[c8 * 8 + 2 * k] - msub), p1 = fta_exp2(s[c8 * 8 + 2 * k + 1] - msub);
-            psum += p0 + p1;
-            pk[k] = FtaType<T>::pack(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        for (int c2 = 0; c2 < FTA_TILE / 2; ++c2) {
+          const float2 e = ffma2(make_float2(s[2 * c2], s[2 * c2 + 1]), make_float2(mul, mul), make_float2(nsub, nsub));
+          const float p0 = fta_exp2(e.x), p1 = fta_exp2(e.y);
+          ps[c2 & 3] += p0 + p1;
+          pk[c2] = FtaType<T>::pack(p0, p1);
         }
-        l += psum;
-        // V rows past the end of the sequence: zero them so that 0 * padding cannot give NaN
-        if (!is_tree && valid < FTA_TILE) {
-          ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x303);
+        l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        if (i >= 2) {  // P[t&1] was the A operand of PV(t-2)
+          ok = wait_all(BAR(B_ODONE + ((t - 2) & 3)), ((t - 2) >> 2) & 1, abort_flag, 0x305);
           if (!ok) break;
-          uint8_t* sV = sm + OFF_RING + st * kStage + kKBytes;
-          const int nz = (FTA_TILE - valid) * 16;
-          for (int idx = tid - 64; idx < nz; idx += 128) {
-            const int rr = valid + (idx >> 4), hc = idx & 15;
-            *reinterpret_cast<uint4*>(sV + (hc >> 3) * kKVHalf + rr * 128 + (hc & 7) * 16) = make_uint4(0, 0, 0, 0);
-          }
         }
-        fence_proxy_async();
+        tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
+        if (!is_tree && valid < FTA_TILE) {
+          ok = zero_v_tail(t, valid);
+          if (!ok) break;
+        }
+        tmem_st_wait();
         tc_fence_before();
         mbar_arrive(BAR(B_PREADY + sbuf));
       }
       if (!ok) break;
 
       // ---- epilogue of the piece: O row / l, LSE ------------------------------------------
-      const uint32_t t_last = gt + n - 1;
-      ok = wait_all(BAR(B_ODONE), t_last & 1, abort_flag, 0x304);
+      ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x304);
       if (!ok) break;
       tc_fence_after();
       float o[kD];
@@ -390,6 +511,12 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(BAR(B_OFREE));
+      // hand the next piece's Q to the MMA issuer before spending time on this piece's stores
+      nhave = w.next(nseg);
+      if (nhave) {
+        ok = q_to_tmem();
+        if (!ok) break;
+      }
 
       if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 0 && row == 0) {
         int2* udesc = reinterpret_cast<int2*>(ws_l + (long long)2 * g.grid * g.R);
@@ -422,9 +549,20 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
       }
       gt += n;
+      seg = nseg;
+      have = nhave;
     }
   }
 
+#ifdef FTA_UMMA_PROFILE
+  if (tid == 0) {
+    unsigned long long gt1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
+    if (blockIdx.x == 0) atomicAdd(&g_umma_prof[159], (unsigned long long)(clock64() - prof_t0));
+    atomicMax(&g_umma_prof[158], (unsigned long long)(clock64() - prof_t0));
+    atomicMax(&g_umma_prof[157], gt1 - prof_g0);
+  }
+#endif
   // ---- teardown -------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -531,14 +669,18 @@ int fta_umma_supported(const FtaParams& p) {
 
 cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStream_t st, int query_only,
                                    int* blocks_per_sm) {
-  auto kern = p.dtype == FTA_DTYPE_F16 ? stage1_umma_kernel<__half> : stage1_umma_kernel<__nv_bfloat16>;
-  const size_t smem = (size_t)OFF_PRE + (size_t)(p.B + 1) * sizeof(int) + 1024;
+  // six ring stages when the prefix table leaves room for them, else five
+  const int ns = smem_bytes(6, p.B) <= 227 * 1024 ? 6 : 5;
+  const size_t smem = smem_bytes(ns, p.B);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  static unsigned long long configured[2] = {0ull, 0ull};
+  void (*kern)(const FtaParams, const FtaGeom, const Maps);
+  if (p.dtype == FTA_DTYPE_F16) kern = ns == 6 ? stage1_umma_kernel<__half, 6> : stage1_umma_kernel<__half, 5>;
+  else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6> : stage1_umma_kernel<__nv_bfloat16, 5>;
+  static unsigned long long configured[4] = {0ull, 0ull, 0ull, 0ull};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  const int ti = p.dtype == FTA_DTYPE_F16 ? 0 : 1;
+  const int ti = (p.dtype == FTA_DTYPE_F16 ? 0 : 1) + (ns == 6 ? 0 : 2);
   if (!((configured[ti] >> (dev & 63)) & 1ull)) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
@@ -562,6 +704,15 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
   kern<<<g.grid, kThreads, smem, st>>>(p, g, maps);
   return cudaGetLastError();
 }
+
+#ifdef FTA_UMMA_PROFILE
+extern "C" int fta_umma_prof(unsigned long long* out64) {
+  unsigned long long zero[160] = {0};
+  if (cudaMemcpyFromSymbol(out64, g_umma_prof, sizeof(zero)) != cudaSuccess) return -1;
+  cudaMemcpyToSymbol(g_umma_prof, zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 // Reads and clears the device status word: 0, or the code of the first bounded wait that gave up.
 extern "C" int fta_umma_status(void) {

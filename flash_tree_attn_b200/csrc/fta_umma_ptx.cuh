@@ -38,7 +38,28 @@ constexpr long long kWaitCycles = 1000000000ll;  // about half a second
 
 __device__ unsigned int g_umma_status = 0u;
 
+
+#ifdef FTA_UMMA_PROFILE
+// development aid: cycles block 0 spends in each wait site (code & 0xff, role = code >> 8)
+__device__ unsigned long long g_umma_prof[160];
+#define FTA_PROF_ADD(code, cycles)                                                                   \
+  do {                                                                                               \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0)                                                  \
+      atomicAdd(&g_umma_prof[(((code) >> 8) & 3) * 32 + ((code) & 31)], (unsigned long long)(cycles)); \
+  } while (0)
+#else
+#define FTA_PROF_ADD(code, cycles) do {} while (0)
+#endif
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code) {
+#ifdef FTA_UMMA_PROFILE
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) { FTA_PROF_ADD(code, clock64() - t0); return true; }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicCAS(&g_umma_status, 0u, code); return false; }
+  }
+#else
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -52,6 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+#endif
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -59,6 +81,13 @@ __device__ __forceinline__ void fence_barrier_init() {
 }
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 
 // ---- TMA -------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -107,7 +136,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// two fused multiply-adds in one instruction (packed fp32 pairs, sm_100)
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
 
 // ---- tcgen05.mma -------------------------------------------------------------------------------
 // Shared-memory operand descriptor, 128-byte swizzle (layout code 2), descriptor version 1.
@@ -141,6 +188,14 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// same product with the A operand read from TMEM (16-bit pairs, one pair per 32-bit column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // arrives on the mbarrier when every tcgen05.mma issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
