@@ -1,0 +1,108 @@
+"""CPU: the multi-rank host logic (sharding, packing, one all-gather, merge) on two gloo ranks,
+with the oracle standing in for the CUDA operator and merge kernel."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import load_golden
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _oracle_decode(q, k, v, ck, cv, mask, lens, block_size, G, with_tree):
+    from oracle.tree_attention_oracle import tree_attention_oracle
+
+    o = tree_attention_oracle(q, k, v, ck, cv, mask, lens, None, G, with_tree=with_tree)
+    return o["out"], o["lse"]
+
+
+def _oracle_merge(po, pl, out_dtype):
+    from oracle.tree_attention_oracle import merge_partials_oracle
+
+    o, l = merge_partials_oracle(po, pl)
+    return o.to(out_dtype), l
+
+
+def _worker(rank, world, port, fail_rank, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        from flash_tree_attn_b200.dist import kv_range_decode, kv_ranges
+        from oracle.tree_attention_oracle import tree_attention_oracle
+
+        g = load_golden("cfg1")
+        lens = g["kv_seq_len"]
+        ctx = g["k_cache"].size(2)
+        lo, hi = kv_ranges(ctx, world, align=16)[rank]
+        shard_len = torch.clamp(lens - lo, min=0, max=hi - lo).to(torch.int32)
+        if rank == fail_rank:
+            raise RuntimeError("injected failure before the collective")
+        out, lse = kv_range_decode(g["q"], g["k_cache"][:, :, lo:hi], g["v_cache"][:, :, lo:hi], g["current_k"],
+                                   g["current_v"], g["mask"], shard_len, 64, 1, out_dtype=torch.float32,
+                                   decode_fn=_oracle_decode, merge_fn=_oracle_merge)
+        whole = tree_attention_oracle(g["q"], g["k_cache"], g["v_cache"], g["current_k"], g["current_v"], g["mask"],
+                                      lens, None, 1)
+        ret[rank] = ((out - whole["out"]).abs().max().item(), (lse - whole["lse"]).abs().max().item())
+    except Exception as e:  # the test inspects what each rank saw
+        ret[rank] = repr(e)
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, fail_rank=-1):
+    port = _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, port, fail_rank, ret), nprocs=world, join=True)
+    return dict(ret)
+
+
+def test_kv_range_decode_two_ranks_matches_whole_sequence():
+    ret = _run(2)
+    for r in range(2):
+        assert isinstance(ret[r], tuple), ret[r]
+        assert ret[r][0] < 1e-5 and ret[r][1] < 1e-5
+
+
+def test_rank_failing_before_the_collective_is_reported_not_hung():
+    """A rank that raises before the all-gather: the survivor's collective ends with an error
+    (peer gone / process-group timeout) instead of hanging."""
+    ret = _run(2, fail_rank=1)
+    assert "injected failure" in ret[1]
+    assert isinstance(ret[0], str), "the surviving rank must see an error, not a result"
+
+
+def test_shard_batch_balances_ragged_lengths():
+    from flash_tree_attn_b200.dist import shard_batch
+    from flash_tree_attn_b200.workloads import WORKLOADS, draw_lengths
+
+    lens = draw_lengths(WORKLOADS["cfg5"])
+    for world in (2, 4, 8):
+        parts = shard_batch(lens, world)
+        assert sorted(i for p in parts for i in p) == list(range(len(lens)))
+        loads = [sum(lens[i] for i in p) for p in parts]
+        assert max(loads) - min(loads) <= max(lens)
+        assert max(loads) <= 1.1 * sum(lens) / world
+
+
+def test_kv_ranges_cover_the_sequence():
+    from flash_tree_attn_b200.dist import kv_ranges
+
+    for L in (1, 63, 64, 100, 131072):
+        for world in (1, 2, 4, 8):
+            r = kv_ranges(L, world)
+            assert r[0][0] == 0 and r[-1][1] == L
+            assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
+            assert all(lo % 64 == 0 for lo, _ in r if lo < L)
