@@ -70,6 +70,8 @@ SYMBOLS = {
     "fta_last_cuda_error": (C.c_char_p, []),
     "fta_workspace_bytes": (_i64, [C.POINTER(FtaParams)]),
     "fta_decode": (C.c_int, [C.POINTER(FtaParams), _vp]),
+    "fta_decode_static": (C.c_int, [C.POINTER(FtaParams), _vp]),
+    "fta_static_scratch_bytes": (_i64, []),
     "fta_stage1": (C.c_int, [C.POINTER(FtaParams), _vp]),
     "fta_stage2": (C.c_int, [C.POINTER(FtaParams), _vp]),
     "fta_merge_parts": (C.c_int, [C.POINTER(FtaMergeParams), _vp]),

@@ -18,7 +18,16 @@ int fta_umma_supported(const FtaParams&);
 cudaError_t fta_launch_stage2(const FtaParams&, const FtaGeom&, cudaStream_t);
 cudaError_t fta_launch_merge_parts(const FtaMergeParams&, cudaStream_t);
 
+// Scratch of fta_decode_static: partial results of the BALANCED plan live here instead of in a
+// caller-provided workspace.  The array is part of the library image: every GPU that loads the
+// library keeps these bytes until the process exits.  In host code the name below is only a
+// stand-in for the symbol; the device address is fetched per device with cudaGetSymbolAddress.
+#define FTA_STATIC_SCRATCH_BYTES (24u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[FTA_STATIC_SCRATCH_BYTES];
+
 namespace {
+
+void* g_static_scratch_ptr[64];  // device address of g_static_scratch, per device ordinal
 
 thread_local char g_cuda_err[256] = "";
 
@@ -230,6 +239,38 @@ int fta_decode(const FtaParams* p, void* stream) {
   rc = run_stage1(*p, g, (cudaStream_t)stream);
   if (rc) return rc;
   cudaError_t e = fta_launch_stage2(*p, g, (cudaStream_t)stream);
+  return e == cudaSuccess ? FTA_OK : cuda_fail(e);
+}
+
+int64_t fta_static_scratch_bytes(void) { return (int64_t)FTA_STATIC_SCRATCH_BYTES; }
+
+int fta_decode_static(const FtaParams* p, void* stream) {
+  if (!p) return FTA_E_BADARG;
+  if (p->split_mode != FTA_SPLIT_BALANCED) return FTA_E_UNSUPPORTED;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return FTA_E_UNSUPPORTED;
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // first call on this device (made with the device current): resolve the symbol's address
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (ptr == nullptr) return FTA_E_CUDA;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  FtaParams q = *p;
+  q.workspace = g_static_scratch_ptr[dev];
+  q.workspace_bytes = (int64_t)FTA_STATIC_SCRATCH_BYTES;
+  int rc = validate(&q);
+  if (rc) return rc;
+  FtaGeom g;
+  rc = make_geom(q, g, true);
+  if (rc) return rc;
+  if (ws_bytes(q, g) > (int64_t)FTA_STATIC_SCRATCH_BYTES) return FTA_E_TOO_LARGE;
+  rc = run_stage1(q, g, (cudaStream_t)stream);
+  if (rc) return rc;
+  e = fta_launch_stage2(q, g, (cudaStream_t)stream);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 

@@ -37,7 +37,7 @@ extern "C" {
 #define FTA_E_UNSUPPORTED 2 /* a valid request this build has no kernel for         */
 #define FTA_E_WORKSPACE 3   /* workspace / mid buffers too small for the plan       */
 #define FTA_E_CUDA 4        /* a CUDA runtime or driver call failed                 */
-#define FTA_E_TOO_LARGE 5   /* request exceeds the static scratch of fta_*_static   */
+#define FTA_E_TOO_LARGE 5   /* request exceeds the fixed scratch of fta_decode_static */
 
 /* ---- enums ------------------------------------------------------------------------- */
 #define FTA_DTYPE_F16 0
@@ -167,6 +167,32 @@ int64_t fta_workspace_bytes(const FtaParams* p);
  * `stream` is a cudaStream_t.
  */
 int fta_decode(const FtaParams* p, void* stream);
+
+/*
+ * fta_decode for callers that cannot allocate device memory: a serving runtime that owns the
+ * whole device heap and hands none of it out, a plugin loaded into a host process whose
+ * allocator it must not touch, code that runs where cudaMalloc is forbidden (inside a stream
+ * capture, after the framework has frozen its memory plan).  The caller passes inputs and
+ * outputs as for fta_decode; `workspace` and `workspace_bytes` are ignored.  The partial
+ * results go to a fixed array inside the library, fta_static_scratch_bytes() bytes (24 MiB)
+ * that every GPU loading the library holds until the process exits.  It has no counterpart in
+ * the reference, which allocates its partial buffers with torch.empty on every call.
+ *
+ *  - Only the BALANCED plan is served.  A request whose partial results do not fit the array
+ *    (very large B * Hkv) is refused with FTA_E_TOO_LARGE; nothing is launched.
+ *  - The first call on a device looks up the array's device address (no allocation); make that
+ *    first call with the device current and before any stream capture begins.
+ *  - All calls on a device share the one array and it keeps whatever the last call left there.
+ *    Nothing in it has to start at zero: stage 1 writes every slot stage 2 reads.  Two calls
+ *    whose kernels overlap on the GPU (different streams) race on it; serialise them.
+ *  - Neither this function nor anything it calls uses cudaMalloc, cudaFree or an allocating
+ *    library routine.
+ */
+int fta_decode_static(const FtaParams* p, void* stream);
+
+/* Size in bytes of the array fta_decode_static keeps its partial results in.  No counterpart in
+   the reference. */
+int64_t fta_static_scratch_bytes(void);
 
 /* Stage 1 alone (flash_tree_attn.py:301-334 plus the tail :367-371). */
 int fta_stage1(const FtaParams* p, void* stream);
