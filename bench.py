@@ -151,6 +151,86 @@ def reference_arm(args, w):
     }))
 
 
+def seq_split_arm(args, w, fta, dev, rank, world, dist):
+    """One long sequence on N GPUs (cfg4): every rank owns a contiguous KV range, computes an fp32
+    partial (O, LSE), ONE all-gather moves the packed partials, the merge kernel runs on every
+    rank.  Strong scaling: the job is the same call at every N."""
+    from flash_tree_attn_b200 import dist as fdist
+    from flash_tree_attn_b200.workloads import draw_lengths, flops, kv_bytes, make_inputs
+
+    lens = draw_lengths(w)
+    inp = make_inputs(w, dev, lens=lens)
+    lo, hi = fdist.kv_ranges(w.ctx, world)[rank]
+    k_sh, v_sh = inp["k_cache"][:, :, lo:hi], inp["v_cache"][:, :, lo:hi]
+    shard_len = torch.tensor([max(0, min(lens[0], hi) - lo)], dtype=torch.int32, device=dev)
+
+    def step(q, ck, cv, mask):
+        return fdist.kv_range_decode(q, k_sh, v_sh, ck, cv, mask, shard_len, w.block_size, w.G)
+
+    def sync():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    a = (inp["q"], inp["current_k"], inp["current_v"], inp["mask"])
+    for _ in range(args.warmup):
+        step(*a)
+    sync()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(*a)
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    # end to end: the step's inputs come from pinned host memory, the result goes back
+    names = ["q", "current_k", "current_v", "mask"]
+    host = {n: inp[n].cpu().pin_memory() for n in names}
+    stage = {n: torch.empty_like(inp[n]) for n in names}
+    out_host = torch.empty((w.B, w.H, w.Q, w.D), dtype=w.dtype).pin_memory()
+    x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    x0.record()
+    for _ in range(args.steps):
+        for n in names:
+            stage[n].copy_(host[n], non_blocking=True)
+        o, _ = step(stage["q"], stage["current_k"], stage["current_v"], stage["mask"])
+        out_host.copy_(o, non_blocking=True)
+    x1.record()
+    sync()
+    ms_e2e = x0.elapsed_time(x1)
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t[0]), float(t[1])
+    if rank == 0:
+        hbm_peak, tf_peak, peak_src = measured_peaks()
+        kvb = kv_bytes(w, lens)
+        calls_s = args.steps / (ms * 1e-3)
+        tfl = flops(w, lens) * calls_s / 1e12
+        print(json.dumps({
+            "metric": "tree_attn_calls_per_s", "value": calls_s, "unit": "calls/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload_config(w, lens), parallelism=f"kv-range x{world}, one all-gather + merge per call"),
+            "kv_read_gbs": kvb * calls_s / 1e9, "tflops": tfl,
+            "roofline": {"bound": "tensor", "achieved": tfl, "peak": tf_peak * world, "unit": "TFLOP/s",
+                         "frac": tfl / (tf_peak * world), "traffic": None, "peak_source": peak_src,
+                         "kernel": "whole call (stage 1 + all-gather + merge)"},
+            "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "calls/s",
+                    "h2d_bytes_per_step": sum(host[n].numel() * host[n].element_size() for n in names),
+                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
+                    "note": "per-rank copies of q / tree K,V / mask from pinned host memory, result copied back; "
+                            "KV cache shards resident in HBM"},
+            "gpu_launches": 3 * args.steps, "clocks": clocks,
+        }))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def workload_config(w, lens):
     return {
         "workload": f"{w.name}: B={w.B} H={w.H} kv_group_num={w.G} D={w.D} q_len={w.Q} "
@@ -202,6 +282,10 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
+
+    if w.lens == "full" and w.B == 1 and world > 1:
+        seq_split_arm(args, w, fta, dev, rank, world, dist)
+        return
 
     # each rank holds its own batch of the workload's shape (the job's batch, sharded)
     wr = small(w, seed=w.seed + 1000 * rank)

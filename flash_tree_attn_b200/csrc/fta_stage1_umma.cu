@@ -245,7 +245,12 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       for (int i = 0; i < n && ok; ++i) {
         const uint32_t t = gt + i, st = t % NS, sbuf = t & 1;
         if (t >= 2) {
+          // S[t&1] has been read by softmax(t-2); and PV(t-2) is complete, so that whoever sees
+          // S(t) ready may overwrite P[t&1] without asking (the softmax warps have no slack, this
+          // warp has plenty)
           ok = wait_all(BAR(B_PREADY + sbuf), ((t - 2) >> 1) & 1, abort_flag, 0x204);
+          if (!ok) break;
+          ok = wait_all(BAR(B_ODONE + ((t - 2) & 3)), ((t - 2) >> 2) & 1, abort_flag, 0x207);
           if (!ok) break;
         }
         ok = wait_all(BAR(B_KFULL + st), (t / NS) & 1, abort_flag, 0x202);
@@ -425,10 +430,14 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         if (!is_tree && valid == FTA_TILE && scale2 > 0.f) {
           float mx[8];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) mx[c] = s[c];
+          for (int c = 0; c < 8; ++c) mx[c] = fmax3(s[c], s[c + 8], s[c + 16]);
 #pragma unroll
-          for (int c = 8; c < FTA_TILE; ++c) mx[c & 7] = fmaxf(mx[c & 7], s[c]);
-          mt = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
+          for (int c = 0; c < 8; ++c) mx[c] = fmax3(mx[c], s[c + 24], s[c + 32]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) mx[c] = fmax3(mx[c], s[c + 40], s[c + 48]);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], s[c + 56]);
+          mt = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
           mul = scale2;
         } else {
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -481,15 +490,16 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
         for (int c2 = 0; c2 < FTA_TILE / 2; ++c2) {
           const float2 e = ffma2(make_float2(s[2 * c2], s[2 * c2 + 1]), make_float2(mul, mul), make_float2(nsub, nsub));
-          const float p0 = fta_exp2(e.x), p1 = fta_exp2(e.y);
+          // every other pair is exponentiated on the FMA pipe, so that the MUFU (4 lanes per
+          // clock) and the FMA pipe work side by side
+          float p0, p1;
+          if (c2 & 1) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
+          else { p0 = fta_exp2(e.x); p1 = fta_exp2(e.y); }
           ps[c2 & 3] += p0 + p1;
           pk[c2] = FtaType<T>::pack(p0, p1);
         }
         l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-        if (i >= 2) {  // P[t&1] was the A operand of PV(t-2)
-          ok = wait_all(BAR(B_ODONE + ((t - 2) & 3)), ((t - 2) >> 2) & 1, abort_flag, 0x305);
-          if (!ok) break;
-        }
+        // P[t&1] was the A operand of PV(t-2), which completed before S(t) was even issued
         tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
         if (!is_tree && valid < FTA_TILE) {
           ok = zero_v_tail(t, valid);

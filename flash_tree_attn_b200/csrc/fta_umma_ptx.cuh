@@ -156,6 +156,34 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   return d;
 }
 
+// exp2 of two values on the FMA and integer pipes (no MUFU): round to the nearest integer n with
+// the 1.5*2^23 trick, 2^f for f = x - n in [-0.5, 0.5] by a degree-4 polynomial (relative error
+// 2.7e-6), then n added into the exponent field.  Inputs below -126 (including -inf) give ~0.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 one = make_float2(1.f, 1.f);
+  const float2 t = ffma2(x, one, make_float2(kMagic, kMagic));
+  const float2 r = ffma2(t, one, make_float2(-kMagic, -kMagic));
+  const float2 f = ffma2(r, make_float2(-1.f, -1.f), x);
+  float2 q = ffma2(make_float2(0.009570101276040077f, 0.009570101276040077f), f,
+                   make_float2(0.05591785907745361f, 0.05591785907745361f));
+  q = ffma2(q, f, make_float2(0.240247443318367f, 0.240247443318367f));
+  q = ffma2(q, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+  q = ffma2(q, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+  float2 y;
+  y.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  y.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return y;
+}
+// maximum of three (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // ---- tcgen05.mma -------------------------------------------------------------------------------
 // Shared-memory operand descriptor, 128-byte swizzle (layout code 2), descriptor version 1.
 //   addr : start address (may be advanced inside a swizzle atom along K for K-major operands)
