@@ -142,7 +142,8 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
   g.n_tree = p.with_tree ? fta_cdiv(p.Q, FTA_TILE) : 0;
   g.min_per = 2;
   g.fixed_max_splits = (p.split_mode == FTA_SPLIT_FIXED && p.split_tokens > 0) ? fta_cdiv(p.ctx, p.split_tokens) : 0;
-  g.pad_ = fam;
+  g.family = fam;
+  g.cs = (fam == FTA_KERNEL_UMMA && g.hpt * g.qpt <= 64) ? 2 : 1;
   g.grid = p.grid_override > 0 ? p.grid_override : 1;
   if (!need_grid || p.grid_override > 0) return FTA_OK;
 
@@ -169,7 +170,7 @@ int64_t ws_bytes(const FtaParams& p, const FtaGeom& g) {
 
 int run_stage1(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
   if (p.split_mode == FTA_SPLIT_BALANCED && p.workspace_bytes < ws_bytes(p, g)) return FTA_E_WORKSPACE;
-  cudaError_t e = g.pad_ == FTA_KERNEL_UMMA ? fta_launch_stage1_umma(p, g, st, 0, nullptr)
+  cudaError_t e = g.family == FTA_KERNEL_UMMA ? fta_launch_stage1_umma(p, g, st, 0, nullptr)
                                             : launch_mma(p, g, st, 0, nullptr);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }

@@ -30,7 +30,8 @@ struct FtaGeom {
   int grid;    // thread blocks launched (BALANCED: resident blocks)
   int min_per; // smallest tile range a block is given (BALANCED)
   int fixed_max_splits; // FIXED: ceil(ctx / split_tokens)
-  int pad_;
+  int family;  // FTA_KERNEL_MMA or FTA_KERNEL_UMMA
+  int cs;      // tcgen05 family: column split (2 when a unit has at most 64 query rows, else 1)
 };
 
 // One contiguous piece of one unit, processed by one block without interruption.

@@ -16,6 +16,13 @@
 //               mask, running max with lazy rescale of O, exp2, P (16-bit pairs) stored to
 //               TMEM; at the end of a piece the normalised O row and its LSE
 //
+// Column split (template CS = 2): when a unit has at most 64 query rows (q_len 64 without GQA),
+// rows 64..127 of the tile repeat rows 0..63 (Q is loaded twice) and each half of the tile's rows
+// works on its own 32 of every tile's 64 KV columns, with its own running max, row sum and O rows.
+// Half of each P row is then zero, the two O halves are two partial attentions of the same query
+// and are merged through shared memory at the end of a piece.  The tensor work is unchanged (the
+// tile has 128 rows either way) but all four schedulers share the exponentials.
+//
 // It replaces the reference's _flash_decoding_fwd_kernel (flash_tree_attn.py:14-144) and the
 // eager tree tail (flash_tree_attn.py:367-371) for head_dim 128 when M = G*Q is large enough
 // to fill a 128-row tile usefully; the work plan, the partial-result slots and the epilogue
@@ -47,13 +54,16 @@ constexpr uint32_t kColS = 128;  // + 64 * buffer
 constexpr uint32_t kColQ = 256;  // 64 columns: 128 head-dim elements, two per column
 constexpr uint32_t kColP = 320;  // + 32 * buffer: 64 KV columns, two per column
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
-constexpr size_t smem_bytes(int ns, int B) { return (size_t)OFF_RING + (size_t)ns * kStage + kBarBytes + (size_t)(B + 1) * 4 + 1024; }
+constexpr uint32_t kXBytes = 64 * 128 * 4 + 64 * 2 * 4;  // CS = 2: one unnormalised O half + (m, l) per query row
+constexpr size_t smem_bytes(int ns, int B, int cs) {
+  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + (size_t)(B + 1) * 4 + 1024;
+}
 
 // mbarrier slots (ring barriers are sized for the largest ring)
 constexpr int kMaxNS = 6;
 enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
        B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + 2,
-       B_FINAL = B_PREADY + 2, B_COUNT = B_FINAL + 2 };
+       B_FINAL = B_PREADY + 2, B_XFULL = B_FINAL + 2, B_XFREE, B_COUNT };
 // A parity wait is only meaningful while the barrier is at most one phase ahead of the phase
 // asked for.  PV(t) therefore commits to B_ODONE + (t & 3): whoever has seen S(t') ready knows
 // that PV(t'-4) and everything before it is complete, so for t in [t'-3, t'] the barrier of PV(t)
@@ -127,10 +137,11 @@ __device__ __forceinline__ int seg_cache_tiles(const FtaSeg& s) {
   return s.c1 > s.c0 ? fta_cdiv(s.c1 - s.c0, FTA_TILE) : 0;
 }
 
-template <typename T, int NS>
+template <typename T, int NS, int CS>
 __global__ void __launch_bounds__(kThreads, 1)
 stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ Maps maps) {
-  constexpr uint32_t OFF_BAR = OFF_RING + NS * kStage;
+  constexpr uint32_t OFF_X = OFF_RING + NS * kStage;
+  constexpr uint32_t OFF_BAR = OFF_X + (CS == 2 ? kXBytes : 0);
   constexpr uint32_t OFF_PRE = OFF_BAR + kBarBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -169,6 +180,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     }
     mbar_init(BAR(B_FINAL), 1);
     mbar_init(BAR(B_FINAL + 1), 1);
+    mbar_init(BAR(B_XFULL), 64);
+    mbar_init(BAR(B_XFREE), 64);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -202,10 +215,13 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           if (u == q_at) {
             ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
             if (!ok) break;
-            mbar_expect_tx(BAR(B_QFULL), 2u * (uint32_t)(g.qpt * g.hpt) * 128u);
+            mbar_expect_tx(BAR(B_QFULL), 2u * CS * (uint32_t)(g.qpt * g.hpt) * 128u);
             const int h0 = unit.kvh * G + unit.gt * g.hpt, q0 = unit.qt * g.qpt;
-            tma_load_4d(base + OFF_Q, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
-            tma_load_4d(base + OFF_Q + kQHalf, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
+#pragma unroll
+            for (int dup = 0; dup < CS; ++dup) {  // CS = 2: the same rows again at tile rows 64..
+              tma_load_4d(base + OFF_Q + dup * 64 * 128, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
+              tma_load_4d(base + OFF_Q + kQHalf + dup * 64 * 128, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
+            }
           }
           for (int which = 0; which < 2; ++which) {  // 0: K of tile u, 1: V of tile u - 2
             const int i = which == 0 ? u : u - 2;
@@ -320,7 +336,22 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     // ================================ softmax / epilogue ===========================
     const int quad = warp & 3;  // the TMEM lane quadrant a warp may touch is fixed by its index
     const int row = quad * 32 + lane;
+    constexpr int NC = FTA_TILE / CS;            // KV columns of a tile this thread works on
+    const int lrow = CS == 2 ? (row & 63) : row;  // query row of the unit this thread works for
+    const int chalf = CS == 2 ? (row >> 6) : 0;  // which NC columns of each tile
+    const int cbase = NC * chalf;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+    uint32_t xcount = 0;  // CS = 2: pieces whose halves have been exchanged so far
+    if (CS == 2) {
+      // the half of every P row this thread never writes must read as zero
+      uint32_t z[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) z[k] = 0u;
+      tmem_st16(t_lane + kColP + 16 * (chalf ^ 1), z);
+      tmem_st16(t_lane + kColP + 32 + 16 * (chalf ^ 1), z);
+      tmem_st_wait();
+      tc_fence_before();
+    }
     const float scale2 = p.sm_scale * FTA_LOG2E;
     float* ws_o = reinterpret_cast<float*>(p.workspace);
     float* ws_l = ws_o + (long long)2 * g.grid * g.R * kD;
@@ -370,7 +401,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       const FtaUnit unit = fta_unit(g, seg.j);
       const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
       int h, qi;
-      const bool rvalid = fta_row(p, g, unit, row, h, qi);
+      const bool rvalid = fta_row(p, g, unit, lrow, h, qi);
       const float* mrow = (rvalid && g.n_tree) ? p.mask + seg.b * p.m_sb + h * p.m_sh + qi * p.m_sq : nullptr;
       float m_used = -INFINITY, l = 0.f;
       const uint32_t t_last = gt + n - 1;
@@ -398,6 +429,18 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x314);
         if (!ok) break;
         mbar_arrive(BAR(B_OFREE));
+        if (CS == 2) {  // keep the halves' exchange barriers in step
+          if (chalf == 1) {
+            ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x315);
+            if (!ok) break;
+            mbar_arrive(BAR(B_XFULL));
+          } else {
+            ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x316);
+            if (!ok) break;
+            mbar_arrive(BAR(B_XFREE));
+          }
+          ++xcount;
+        }
         gt += n;
         have = w.next(seg);
         if (have) ok = q_to_tmem();
@@ -418,9 +461,9 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           valid = p.Q - col0 < FTA_TILE ? p.Q - col0 : FTA_TILE;
         }
         tc_fence_after();
-        float s[FTA_TILE];
-        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf, s);
-        tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + 32, s + 32);
+        float s[NC];
+#pragma unroll
+        for (int k = 0; k < NC / 32; ++k) tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + cbase + 32 * k, s + 32 * k);
         tmem_ld_wait();
 
         // Row maximum in the log2 domain (mt) and the factor `mul` that takes s[] there.
@@ -432,28 +475,29 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
           for (int c = 0; c < 8; ++c) mx[c] = fmax3(s[c], s[c + 8], s[c + 16]);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) mx[c] = fmax3(mx[c], s[c + 24], s[c + 32]);
+          for (int c = 24; c + 8 < NC; c += 16)
 #pragma unroll
-          for (int c = 0; c < 8; ++c) mx[c] = fmax3(mx[c], s[c + 40], s[c + 48]);
+            for (int k = 0; k < 8; ++k) mx[k] = fmax3(mx[k], s[c + k], s[c + 8 + k]);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], s[c + 56]);
+          for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], s[NC - 8 + c]);
           mt = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
           mul = scale2;
         } else {
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          const int vh = valid - cbase;  // valid columns among this thread's
           if (is_tree && mrow != nullptr) {
 #pragma unroll
-            for (int c = 0; c < FTA_TILE; ++c) {
+            for (int c = 0; c < NC; ++c) {
               float v = s[c] * scale2;
-              if (c < valid) v += __ldg(mrow + col0 + c) * FTA_LOG2E;
+              if (c < vh) v += __ldg(mrow + col0 + cbase + c) * FTA_LOG2E;
               else v = -INFINITY;
               s[c] = v;
               mx[c & 3] = fmaxf(mx[c & 3], v);
             }
           } else {
 #pragma unroll
-            for (int c = 0; c < FTA_TILE; ++c) {
-              const float v = c < valid ? s[c] * scale2 : -INFINITY;
+            for (int c = 0; c < NC; ++c) {
+              const float v = c < vh ? s[c] * scale2 : -INFINITY;
               s[c] = v;
               mx[c & 3] = fmaxf(mx[c & 3], v);
             }
@@ -486,9 +530,9 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         }
         const float nsub = m_used == -INFINITY ? 0.f : -m_used;
         float ps[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[FTA_TILE / 2];
+        uint32_t pk[NC / 2];
 #pragma unroll
-        for (int c2 = 0; c2 < FTA_TILE / 2; ++c2) {
+        for (int c2 = 0; c2 < NC / 2; ++c2) {
           const float2 e = ffma2(make_float2(s[2 * c2], s[2 * c2 + 1]), make_float2(mul, mul), make_float2(nsub, nsub));
           // every other pair is exponentiated on the FMA pipe, so that the MUFU (4 lanes per
           // clock) and the FMA pipe work side by side
@@ -500,7 +544,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         }
         l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
         // P[t&1] was the A operand of PV(t-2), which completed before S(t) was even issued
-        tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
+        if (CS == 2) tmem_st16(t_lane + kColP + 32 * sbuf + 16 * chalf, pk);
+        else tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
         if (!is_tree && valid < FTA_TILE) {
           ok = zero_v_tail(t, valid);
           if (!ok) break;
@@ -527,12 +572,47 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         ok = q_to_tmem();
         if (!ok) break;
       }
+      if (CS == 2) {
+        // The two halves of the tile's rows hold two partial attentions of the same queries (over
+        // the lower / upper 32 columns of every tile).  The upper half parks its unnormalised O row,
+        // maximum and row sum in shared memory (16-byte chunks XOR-swizzled by row: conflict-free);
+        // the lower half folds them into its own and goes on to store the result.
+        float* xo = reinterpret_cast<float*>(sm + OFF_X);
+        float* xm = xo + 64 * 128;
+        if (chalf == 1) {
+          ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x30a);
+          if (!ok) break;
+#pragma unroll
+          for (int j = 0; j < kD / 4; ++j)
+            *reinterpret_cast<float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2)) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          xm[2 * lrow] = m_used;
+          xm[2 * lrow + 1] = l;
+          mbar_arrive(BAR(B_XFULL));
+        } else {
+          ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x30b);
+          if (!ok) break;
+          const float m1 = xm[2 * lrow], l1 = xm[2 * lrow + 1];
+          const float mstar = fmaxf(m_used, m1);
+          const float w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
+          const float w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
+#pragma unroll
+          for (int j = 0; j < kD / 4; ++j) {
+            const float4 v = *reinterpret_cast<const float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2));
+            o[4 * j] = o[4 * j] * w0 + v.x * w1; o[4 * j + 1] = o[4 * j + 1] * w0 + v.y * w1;
+            o[4 * j + 2] = o[4 * j + 2] * w0 + v.z * w1; o[4 * j + 3] = o[4 * j + 3] * w0 + v.w * w1;
+          }
+          l = l * w0 + l1 * w1;
+          m_used = mstar;
+          mbar_arrive(BAR(B_XFREE));
+        }
+        ++xcount;
+      }
 
       if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 0 && row == 0) {
         int2* udesc = reinterpret_cast<int2*>(ws_l + (long long)2 * g.grid * g.R);
         udesc[(long long)seg.b * g.U + seg.j] = make_int2(seg.nsplit, (seg.slot >> 1) | ((seg.slot & 1) << 31));
       }
-      if (rvalid) {
+      if (rvalid && chalf == 0) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
         const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
@@ -544,8 +624,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           dst = p.out; dt = p.out_dtype; off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
           if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
         } else if (p.split_mode == FTA_SPLIT_BALANCED) {
-          dst = ws_o; off = ((long long)seg.slot * g.R + row) * kD;
-          ws_l[(long long)seg.slot * g.R + row] = lse;
+          dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
+          ws_l[(long long)seg.slot * g.R + lrow] = lse;
         } else if (tree_piece) {
           const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
           dst = p.tree_o; off = ro * kD;
@@ -679,18 +759,25 @@ int fta_umma_supported(const FtaParams& p) {
 
 cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStream_t st, int query_only,
                                    int* blocks_per_sm) {
-  // six ring stages when the prefix table leaves room for them, else five
-  const int ns = smem_bytes(6, p.B) <= 227 * 1024 ? 6 : 5;
-  const size_t smem = smem_bytes(ns, p.B);
+  // six ring stages when everything else leaves room for them, else five
+  const int cs = g.cs == 2 ? 2 : 1;
+  const int ns = smem_bytes(6, p.B, cs) <= 227 * 1024 ? 6 : 5;
+  const size_t smem = smem_bytes(ns, p.B, cs);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   void (*kern)(const FtaParams, const FtaGeom, const Maps);
-  if (p.dtype == FTA_DTYPE_F16) kern = ns == 6 ? stage1_umma_kernel<__half, 6> : stage1_umma_kernel<__half, 5>;
-  else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6> : stage1_umma_kernel<__nv_bfloat16, 5>;
-  static unsigned long long configured[4] = {0ull, 0ull, 0ull, 0ull};
+  const bool f16 = p.dtype == FTA_DTYPE_F16;
+  if (cs == 2) {
+    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 2> : stage1_umma_kernel<__half, 5, 2>;
+    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 2> : stage1_umma_kernel<__nv_bfloat16, 5, 2>;
+  } else {
+    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 1> : stage1_umma_kernel<__half, 5, 1>;
+    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 1> : stage1_umma_kernel<__nv_bfloat16, 5, 1>;
+  }
+  static unsigned long long configured[8] = {0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  const int ti = (p.dtype == FTA_DTYPE_F16 ? 0 : 1) + (ns == 6 ? 0 : 2);
+  const int ti = (f16 ? 0 : 1) + (ns == 6 ? 0 : 2) + (cs == 2 ? 4 : 0);
   if (!((configured[ti] >> (dev & 63)) & 1ull)) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
