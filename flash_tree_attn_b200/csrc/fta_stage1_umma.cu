@@ -48,11 +48,14 @@ constexpr uint32_t kStage = 2 * kKBytes;      // K tile then V tile
 constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_RING = OFF_Q + kQBytes;
 constexpr uint32_t kBarBytes = 448;
-// TMEM columns (32-bit): O fp32 | S fp32 x2 | Q 16-bit pairs | P 16-bit pairs x2
+// TMEM columns (32-bit): O fp32 | S fp32 x3 | Q 16-bit pairs | P 16-bit pairs x3.  Three S and P
+// buffers let S = Q K^T run three tiles ahead of the softmax and take PV(t-3), not PV(t-2), as the
+// product a new P must not overwrite: neither wait is then ever on the softmax's critical path.
 constexpr uint32_t kTmemCols = 512;
+constexpr int kNBuf = 3;
 constexpr uint32_t kColS = 128;  // + 64 * buffer
-constexpr uint32_t kColQ = 256;  // 64 columns: 128 head-dim elements, two per column
-constexpr uint32_t kColP = 320;  // + 32 * buffer: 64 KV columns, two per column
+constexpr uint32_t kColQ = 320;  // 64 columns: 128 head-dim elements, two per column
+constexpr uint32_t kColP = 384;  // + 32 * buffer: 64 KV columns, two per column
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
 constexpr uint32_t kXBytes = 64 * 128 * 4 + 64 * 2 * 4;  // CS = 2: one unnormalised O half + (m, l) per query row
 constexpr size_t smem_bytes(int ns, int B, int cs) {
@@ -62,8 +65,8 @@ constexpr size_t smem_bytes(int ns, int B, int cs) {
 // mbarrier slots (ring barriers are sized for the largest ring)
 constexpr int kMaxNS = 6;
 enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
-       B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + 2,
-       B_FINAL = B_PREADY + 2, B_XFULL = B_FINAL + 2, B_XFREE, B_COUNT };
+       B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + 3,
+       B_FINAL = B_PREADY + 3, B_XFULL = B_FINAL + 2, B_XFREE, B_COUNT };
 // A parity wait is only meaningful while the barrier is at most one phase ahead of the phase
 // asked for.  PV(t) therefore commits to B_ODONE + (t & 3): whoever has seen S(t') ready knows
 // that PV(t'-4) and everything before it is complete, so for t in [t'-3, t'] the barrier of PV(t)
@@ -174,7 +177,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       mbar_init(BAR(B_KEMPTY + s), 1);
       mbar_init(BAR(B_VEMPTY + s), 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kNBuf; ++s) {
       mbar_init(BAR(B_SFULL + s), 1);
       mbar_init(BAR(B_PREADY + s), 128);
     }
@@ -259,14 +262,13 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
       ok = wait_all(BAR(B_QREADY), sidx & 1, abort_flag, 0x201);  // Q rows are in TMEM
       for (int i = 0; i < n && ok; ++i) {
-        const uint32_t t = gt + i, st = t % NS, sbuf = t & 1;
-        if (t >= 2) {
-          // S[t&1] has been read by softmax(t-2); and PV(t-2) is complete, so that whoever sees
-          // S(t) ready may overwrite P[t&1] without asking (the softmax warps have no slack, this
-          // warp has plenty)
-          ok = wait_all(BAR(B_PREADY + sbuf), ((t - 2) >> 1) & 1, abort_flag, 0x204);
+        const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
+        if (t >= kNBuf) {
+          // S[t%3] has been read by softmax(t-3); and PV(t-3) is complete, so that whoever sees
+          // S(t) ready may overwrite P[t%3] without asking.  Both happened about two tiles ago.
+          ok = wait_all(BAR(B_PREADY + sbuf), ((t - kNBuf) / kNBuf) & 1, abort_flag, 0x204);
           if (!ok) break;
-          ok = wait_all(BAR(B_ODONE + ((t - 2) & 3)), ((t - 2) >> 2) & 1, abort_flag, 0x207);
+          ok = wait_all(BAR(B_ODONE + ((t - kNBuf) & 3)), ((t - kNBuf) >> 2) & 1, abort_flag, 0x207);
           if (!ok) break;
         }
         ok = wait_all(BAR(B_KFULL + st), (t / NS) & 1, abort_flag, 0x202);
@@ -304,8 +306,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     while (ok && w.next(seg)) {
       const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
       for (int i = 0; i < n && ok; ++i) {
-        const uint32_t t = gt + i, st = t % NS, sbuf = t & 1;
-        ok = wait_all(BAR(B_PREADY + sbuf), (t >> 1) & 1, abort_flag, 0x214);  // P(t) is in TMEM
+        const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
+        ok = wait_all(BAR(B_PREADY + sbuf), (t / kNBuf) & 1, abort_flag, 0x214);  // P(t) is in TMEM
         if (!ok) break;
         ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x215);
         if (!ok) break;
@@ -347,8 +349,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       uint32_t z[16];
 #pragma unroll
       for (int k = 0; k < 16; ++k) z[k] = 0u;
-      tmem_st16(t_lane + kColP + 16 * (chalf ^ 1), z);
-      tmem_st16(t_lane + kColP + 32 + 16 * (chalf ^ 1), z);
+#pragma unroll
+      for (int k = 0; k < kNBuf; ++k) tmem_st16(t_lane + kColP + 32 * k + 16 * (chalf ^ 1), z);
       tmem_st_wait();
       tc_fence_before();
     }
@@ -412,8 +414,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if (!working) {
         // a warp whose 32 rows are all M-tile padding only keeps the barrier protocol going
         for (int i = 0; i < n; ++i) {
-          const uint32_t t = gt + i, sbuf = t & 1;
-          ok = wait_all(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x311);
+          const uint32_t t = gt + i, sbuf = t % kNBuf;
+          ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x311);
           if (!ok) break;
           if (i < n_ct) {
             const int row0 = seg.c0 + i * FTA_TILE;
@@ -448,8 +450,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       }
 
       for (int i = 0; i < n; ++i) {
-        const uint32_t t = gt + i, sbuf = t & 1;
-        ok = wait_all(BAR(B_SFULL + sbuf), (t >> 1) & 1, abort_flag, 0x301);
+        const uint32_t t = gt + i, sbuf = t % kNBuf;
+        ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
         if (!ok) break;
         const bool is_tree = i >= n_ct;
         int valid, col0 = 0;
@@ -543,7 +545,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           pk[c2] = FtaType<T>::pack(p0, p1);
         }
         l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-        // P[t&1] was the A operand of PV(t-2), which completed before S(t) was even issued
+        // P[t%3] was the A operand of PV(t-3), which completed before S(t) was even issued
         if (CS == 2) tmem_st16(t_lane + kColP + 32 * sbuf + 16 * chalf, pk);
         else tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
         if (!is_tree && valid < FTA_TILE) {
