@@ -164,8 +164,8 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
 }
 
 int64_t ws_bytes(const FtaParams& p, const FtaGeom& g) {
-  // partial O + partial LSE for two slots per block, then one int2 per unit
-  return (int64_t)2 * g.grid * g.R * (p.D + 1) * 4 + (int64_t)p.B * g.U * 8;
+  // partial O + partial LSE for two slots per stage-1 block, then one int4 per stage-1 block
+  return (int64_t)2 * g.grid * g.R * (p.D + 1) * 4 + (int64_t)g.grid * 16;
 }
 
 int run_stage1(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {

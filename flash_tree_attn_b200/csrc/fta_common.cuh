@@ -43,6 +43,7 @@ struct FtaSeg {
   int split;    // index of this piece among the unit's pieces
   int nsplit;   // pieces of the unit (1 -> the block writes the final result itself)
   int slot;     // BALANCED: workspace slot of the partial
+  int p0slot;   // BALANCED: workspace slot of the unit's first piece
 };
 
 __host__ __device__ __forceinline__ int fta_cdiv(int a, int b) { return (a + b - 1) / b; }
@@ -107,6 +108,7 @@ struct FtaBalanced {
     s.split = c - cfirst;
     s.nsplit = clast - cfirst + 1;
     s.slot = 2 * c + (lin == cbeg ? 0 : 1);
+    s.p0slot = 2 * cfirst + (ustart == (long long)cfirst * per ? 0 : 1);
     return send;
   }
 
@@ -168,6 +170,16 @@ __host__ __device__ __forceinline__ bool fta_row(const FtaParams& p, const FtaGe
 
 #ifdef __CUDACC__
 // ---- device helpers ----------------------------------------------------------------------
+
+// BALANCED workspace: partial O rows [2*grid][R][D] fp32, partial LSEs [2*grid][R] fp32, then one
+// int4 per stage-1 block: the unit whose SECOND piece opens that block, {b, j, pieces, slot of the
+// first piece}, or pieces = 0.  Pieces after the first sit in slot 2*(block of the second piece + i - 1).
+// Stage 2 launches one group of blocks per stage-1 block and merges exactly the units that were cut.
+__device__ __forceinline__ int4* fta_cut_desc(const FtaParams& p, const FtaGeom& g) {
+  float* ws_o = reinterpret_cast<float*>(p.workspace);
+  float* ws_l = ws_o + (long long)2 * g.grid * g.R * p.D;
+  return reinterpret_cast<int4*>(ws_l + (long long)2 * g.grid * g.R);
+}
 
 // Block-cooperative build of the prefix table pre[0..B] in shared memory (warp 0 scans).
 // Must be followed by __syncthreads().

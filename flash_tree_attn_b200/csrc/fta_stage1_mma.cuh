@@ -124,6 +124,7 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
     plan.per = FtaBalanced::choose_per(plan.total, gridDim.x, g.min_per);
     lin = (long long)blockIdx.x * plan.per;
     lin_end = lin + plan.per < plan.total ? lin + plan.per : plan.total;
+    if (tid == 0) fta_cut_desc(p, g)[blockIdx.x] = make_int4(0, 0, 0, 0);  // rewritten below if a cut unit opens this block
   } else {
     item = blockIdx.x;
     n_items = (long long)p.B * g.U * (g.fixed_max_splits + 1);
@@ -364,12 +365,8 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
     const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
     float* ws_o = reinterpret_cast<float*>(p.workspace);
     float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
-    if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 0 && tid == 0) {
-      // tell stage 2 how this unit was cut: {pieces, first block | (first piece in slot 1) << 31}
-      int2* udesc = reinterpret_cast<int2*>(ws_l + (long long)2 * g.grid * g.R);
-      const int cfirst = (seg.slot >> 1);
-      udesc[(long long)seg.b * g.U + seg.j] = make_int2(seg.nsplit, cfirst | ((seg.slot & 1) << 31));
-    }
+    if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 1 && tid == 0)
+      fta_cut_desc(p, g)[blockIdx.x] = make_int4(seg.b, seg.j, seg.nsplit, seg.p0slot);  // for stage 2
     for (int i = tid; i < C::R * (D / 4); i += kThreads) {
       const int row = i / (D / 4), c4 = (i - row * (D / 4)) * 4;
       int h, qi;

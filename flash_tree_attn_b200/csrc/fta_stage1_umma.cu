@@ -396,6 +396,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       return true;
     };
 
+    if (p.split_mode == FTA_SPLIT_BALANCED && row == 0)
+      fta_cut_desc(p, g)[blockIdx.x] = make_int4(0, 0, 0, 0);  // rewritten below if a cut unit opens this block
     FtaSeg seg;
     bool have = w.next(seg);
     if (have) ok = q_to_tmem();
@@ -610,10 +612,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         ++xcount;
       }
 
-      if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 0 && row == 0) {
-        int2* udesc = reinterpret_cast<int2*>(ws_l + (long long)2 * g.grid * g.R);
-        udesc[(long long)seg.b * g.U + seg.j] = make_int2(seg.nsplit, (seg.slot >> 1) | ((seg.slot & 1) << 31));
-      }
+      if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 1 && row == 0)
+        fta_cut_desc(p, g)[blockIdx.x] = make_int4(seg.b, seg.j, seg.nsplit, seg.p0slot);  // for stage 2
       if (rvalid && chalf == 0) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;

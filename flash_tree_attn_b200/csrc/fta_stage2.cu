@@ -34,30 +34,27 @@ struct Acc {
 constexpr int kThreads = 256;
 constexpr int kRowsPerBlock = kThreads / 32;
 
-// One warp per query row, one float4 of head_dim per lane (two for head_dim 256); grid =
-// (units, row groups).  Loads of up to four partials are issued before any is folded in.
+// One warp per query row, one float4 of head_dim per lane (two for head_dim 256).  Loads of up to
+// four partials are issued before any is folded in.
+//   BALANCED: grid = (stage-1 blocks, row groups): block c merges the unit whose second piece
+//             opens stage-1 block c, if any (fta_cut_desc); uncut units were finished by stage 1.
+//   FIXED:    grid = (units, row groups).
 __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, const FtaGeom g) {
-  const int b = blockIdx.x / g.U, j = blockIdx.x - b * g.U;
   const int row = blockIdx.y * kRowsPerBlock + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int D = p.D;
   if (row >= g.R) return;
-  const FtaUnit unit = fta_unit(g, j);
-  int h, qi;
-  if (!fta_row(p, g, unit, row, h, qi)) return;
 
   if (p.split_mode == FTA_SPLIT_BALANCED) {
-    // stage 1 left {pieces, first block | first-slot flag} for every unit that has work
+    const int4 cut = fta_cut_desc(p, g)[blockIdx.x];
+    const int np = cut.z;
+    if (np < 2) return;
+    const int b = cut.x, j = cut.y;
+    const FtaUnit unit = fta_unit(g, j);
+    int h, qi;
+    if (!fta_row(p, g, unit, row, h, qi)) return;
     const float* ws_o = reinterpret_cast<const float*>(p.workspace);
     const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
-    const int2* udesc = reinterpret_cast<const int2*>(ws_l + (long long)2 * g.grid * g.R);
-    int np = 0, cfirst = 0, flag = 0;
-    const bool empty_unit = g.n_tree == 0 && fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx) == 0;
-    if (!empty_unit) {
-      const int2 d = udesc[(long long)b * g.U + j];
-      np = d.x; cfirst = d.y & 0x7fffffff; flag = (d.y >> 31) & 1;
-      if (np == 1) return;  // stage 1 wrote the final rows itself
-    }
     for (int c4 = lane * 4; c4 < D; c4 += 128) {
       Acc acc; acc.init();
       for (int s0 = 0; s0 < np; s0 += 4) {
@@ -67,7 +64,7 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
           const int s = s0 + k;
           lse[k] = -INFINITY; o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (s < np) {
-            const long long slot = 2ll * (cfirst + s) + (s == 0 ? flag : 0);
+            const long long slot = s == 0 ? (long long)cut.w : 2ll * ((long long)blockIdx.x + s - 1);
             lse[k] = ws_l[slot * g.R + row];
             o[k] = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row) * D + c4);
           }
@@ -81,6 +78,10 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
     return;
   }
 
+  const int b = blockIdx.x / g.U, j = blockIdx.x - b * g.U;
+  const FtaUnit unit = fta_unit(g, j);
+  int h, qi;
+  if (!fta_row(p, g, unit, row, h, qi)) return;
   // FIXED: cache partials in mid_o/mid_lse, the tree partial in tree_o/tree_lse
   const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx);
   const int np = fta_cdiv(Lb, p.split_tokens);
@@ -113,6 +114,19 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
   }
 }
 
+// BALANCED without the tree tokens: a sequence of length 0 has no tile at all, so no stage-1 block
+// ever writes its rows; they are defined here (zero output, LSE = -inf).
+__global__ void __launch_bounds__(kThreads) empty_rows_kernel(const FtaParams p) {
+  const int b = blockIdx.x;
+  if (fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx) != 0) return;
+  const int D4 = p.D >> 2;
+  for (int i = threadIdx.x; i < p.H * p.Q * D4; i += kThreads) {
+    const int c4 = (i % D4) * 4, hq = i / D4, qi = hq % p.Q, h = hq / p.Q;
+    fta_store4(p.out, p.out_dtype, b * p.o_sb + h * p.o_sh + qi * p.o_sq + c4, make_float4(0.f, 0.f, 0.f, 0.f));
+    if (c4 == 0 && p.lse) p.lse[b * p.l_sb + h * p.l_sh + qi] = -INFINITY;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) merge_parts_kernel(const FtaMergeParams p) {
   const int D4 = p.D >> 2;
   const long long n = (long long)p.rows * D4;
@@ -131,8 +145,10 @@ __global__ void __launch_bounds__(kThreads) merge_parts_kernel(const FtaMergePar
 }  // namespace
 
 cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
-  const dim3 grid(p.B * g.U, (g.R + kRowsPerBlock - 1) / kRowsPerBlock);
+  const bool balanced = p.split_mode == FTA_SPLIT_BALANCED;
+  const dim3 grid(balanced ? g.grid : p.B * g.U, (g.R + kRowsPerBlock - 1) / kRowsPerBlock);
   stage2_kernel<<<grid, kThreads, 0, st>>>(p, g);
+  if (balanced && !p.with_tree) empty_rows_kernel<<<p.B, kThreads, 0, st>>>(p);
   return cudaGetLastError();
 }
 

@@ -57,11 +57,15 @@ def unpack_partials(buf: torch.Tensor, n: int, o_shape, lse_shape):
     return buf[:, :no].reshape(n, *o_shape), buf[:, no:].reshape(n, *lse_shape)
 
 
-def _default_decode(q, k, v, ck, cv, mask, lens, block_size, kv_group_num, with_tree):
+def _default_decode(q, k, v, ck, cv, mask, lens, block_size, kv_group_num, with_tree, out_buf=None, lse_buf=None):
     from .op import flash_decoding_attention_with_lse
 
     return flash_decoding_attention_with_lse(q, k, v, ck, cv, mask, lens, block_size, None, kv_group_num=kv_group_num,
-                                             out_dtype=torch.float32, with_tree=with_tree)
+                                             out_dtype=torch.float32, with_tree=with_tree, out_buf=out_buf,
+                                             lse_buf=lse_buf)
+
+
+_gather_bufs = {}  # (device, world, numel) -> (mine, gathered), reused across calls
 
 
 def _default_merge(po, pl, out_dtype):
@@ -84,10 +88,22 @@ def kv_range_decode(
     """
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
-    o, lse = decode_fn(q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size, kv_group_num,
-                       rank == world - 1)
-    mine = pack_partial(o, lse)
-    gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=mine.device)
+    B, H, Q, D = q.shape
+    if decode_fn is _default_decode:
+        # the operator writes its partial straight into this rank's slot of the packed buffer
+        no, nl = B * H * Q * D, B * H * Q
+        key = (q.device, world, no + nl)
+        if key not in _gather_bufs:
+            _gather_bufs[key] = (torch.empty(no + nl, dtype=torch.float32, device=q.device),
+                                 torch.empty(world * (no + nl), dtype=torch.float32, device=q.device))
+        mine, gathered = _gather_bufs[key]
+        o, lse = decode_fn(q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size, kv_group_num,
+                           rank == world - 1, out_buf=mine[:no].view(B, H, Q, D), lse_buf=mine[no:].view(B, H, Q))
+    else:
+        o, lse = decode_fn(q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size, kv_group_num,
+                           rank == world - 1)
+        mine = pack_partial(o, lse)
+        gathered = torch.empty(world * mine.numel(), dtype=torch.float32, device=mine.device)
     dist.all_gather_into_tensor(gathered, mine, group=group)
     po, pl = unpack_partials(gathered, world, tuple(o.shape), tuple(lse.shape))
-    return merge_fn(po.contiguous(), pl.contiguous(), out_dtype or q.dtype)
+    return merge_fn(po, pl, out_dtype or q.dtype)

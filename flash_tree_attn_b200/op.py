@@ -115,7 +115,7 @@ class PreparedCall:
 def prepare(
     q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size=64, max_seq_len_in_batch=None,
     output=None, mid_output=None, mid_output_lse=None, sm_scale=None, kv_group_num=1, *,
-    want_lse=False, out_dtype=None, with_tree=True,
+    want_lse=False, out_dtype=None, with_tree=True, out_buf=None, lse_buf=None,
 ) -> PreparedCall:
     """Validate the arguments of flash_decoding_attention and build the C-ABI call without
     launching it."""
@@ -197,10 +197,18 @@ def prepare(
         keep += [current_k, current_v, mask]
 
     out_dtype = q.dtype if out_dtype is None else out_dtype
-    out = torch.empty((B, H, Q, D), dtype=out_dtype, device=dev)
+    if out_buf is not None:  # caller-owned result storage (e.g. a slice of a gather buffer)
+        assert out_buf.dtype == out_dtype and tuple(out_buf.shape) == (B, H, Q, D) and out_buf.is_contiguous()
+        out = out_buf
+    else:
+        out = torch.empty((B, H, Q, D), dtype=out_dtype, device=dev)
     p.out = out.data_ptr(); p.o_sb, p.o_sh, p.o_sq = out.stride(0), out.stride(1), out.stride(2)
     lse = None
-    if want_lse:
+    if want_lse and lse_buf is not None:
+        assert lse_buf.dtype == torch.float32 and tuple(lse_buf.shape) == (B, H, Q) and lse_buf.is_contiguous()
+        lse = lse_buf
+        p.lse = lse.data_ptr(); p.l_sb, p.l_sh = lse.stride(0), lse.stride(1)
+    elif want_lse:
         lse = torch.empty((B, H, Q), dtype=torch.float32, device=dev)
         p.lse = lse.data_ptr(); p.l_sb, p.l_sh = lse.stride(0), lse.stride(1)
 
@@ -329,17 +337,19 @@ def flash_decoding_attention_with_lse(
     q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size=64, max_seq_len_in_batch=None,
     output=None, mid_output=None, mid_output_lse=None, sm_scale=None, kv_group_num=1,
     *, out_dtype: Optional[torch.dtype] = None, with_tree: bool = True,
+    out_buf: Optional[torch.Tensor] = None, lse_buf: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Same operator, also returning the fp32 natural-log LSE [bsz, num_heads, q_len] of the
     merged softmax.  `out_dtype=torch.float32` keeps the result unrounded and
     `with_tree=False` leaves the tree tokens out: together they give the (O, LSE) partial of
-    one KV-range shard, to be merged across shards (see dist.py).  The reference keeps its
-    LSE internal and in 16 bits (flash_tree_attn.py:285,:373).
+    one KV-range shard, to be merged across shards (see dist.py).  `out_buf` / `lse_buf` make
+    the call write into caller-owned contiguous tensors instead of new ones.  The reference
+    keeps its LSE internal and in 16 bits (flash_tree_attn.py:285,:373).
     """
     return _decode(
         q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size, max_seq_len_in_batch,
         output, mid_output, mid_output_lse, sm_scale, kv_group_num,
-        want_lse=True, out_dtype=out_dtype, with_tree=with_tree,
+        want_lse=True, out_dtype=out_dtype, with_tree=with_tree, out_buf=out_buf, lse_buf=lse_buf,
     )
 
 
@@ -351,15 +361,19 @@ def merge_partials(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype: torc
     lib = _lib.load()
     assert part_o.is_cuda and part_o.dtype == torch.float32 and part_lse.dtype == torch.float32
     n, D = part_o.size(0), part_o.size(-1)
-    part_o = part_o.contiguous()
-    part_lse = part_lse.contiguous()
+    # parts may be slices of one gather buffer: each part contiguous, any 16-byte-aligned stride
+    # between parts
+    if not (part_o[0].is_contiguous() and part_o.stride(0) % 4 == 0 and part_o.data_ptr() % 16 == 0):
+        part_o = part_o.contiguous()
+    if not part_lse[0].is_contiguous():
+        part_lse = part_lse.contiguous()
     rows = part_lse[0].numel()
     assert part_o[0].numel() == rows * D
     out = torch.empty(part_o.shape[1:], dtype=out_dtype, device=part_o.device)
     lse = torch.empty(part_lse.shape[1:], dtype=torch.float32, device=part_o.device)
     mp = _lib.FtaMergeParams()
-    mp.part_o = part_o.data_ptr(); mp.po_ss = rows * D
-    mp.part_lse = part_lse.data_ptr(); mp.pl_ss = rows
+    mp.part_o = part_o.data_ptr(); mp.po_ss = part_o.stride(0)
+    mp.part_lse = part_lse.data_ptr(); mp.pl_ss = part_lse.stride(0)
     mp.n_parts, mp.rows, mp.D, mp.out_dtype = n, rows, D, _DT[out_dtype]
     mp.out = out.data_ptr(); mp.lse = lse.data_ptr()
     stream = torch.cuda.current_stream(part_o.device).cuda_stream

@@ -157,7 +157,7 @@ const char* fta_last_cuda_error(void);
  * Bytes of `workspace` a BALANCED call with these sizes needs on the current device.
  * Replaces the reference's per-call torch.empty of mid_output / mid_output_lse
  * (flash_tree_attn.py:276-281); unlike those it does not grow with B or ctx.
- * Only B, H, Hkv, Q, D, dtype, kernel and grid_override are read.
+ * Only H, Hkv, Q, D, dtype, kernel and grid_override are read.
  */
 int64_t fta_workspace_bytes(const FtaParams* p);
 
@@ -179,7 +179,8 @@ int fta_decode(const FtaParams* p, void* stream);
  * the reference, which allocates its partial buffers with torch.empty on every call.
  *
  *  - Only the BALANCED plan is served.  A request whose partial results do not fit the array
- *    (very large B * Hkv) is refused with FTA_E_TOO_LARGE; nothing is launched.
+ *    (a grid_override far above the device's resident-block count) is refused with
+ *    FTA_E_TOO_LARGE; nothing is launched.
  *  - The first call on a device looks up the array's device address (no allocation); make that
  *    first call with the device current and before any stream capture begins.
  *  - All calls on a device share the one array and it keeps whatever the last call left there.

@@ -66,22 +66,24 @@ def test_static_scratch_rejects_oversized_requests():
     from flash_tree_attn_b200 import _lib
 
     lib = _lib.load()
-    # enough (sequence, KV head) units that their descriptors alone exceed the fixed array
-    B, H = 4096, 1024
+    # partial-result slots scale with the number of stage-1 blocks: ask for far more blocks than
+    # the fixed array has room for
+    B, H = 4, 8
     p = _lib.FtaParams()
-    dummy = torch.zeros(64, dtype=torch.float16, device="cuda")
+    dummy = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
     lens = torch.zeros(B, dtype=torch.int32, device="cuda")
     for name in ("q", "k_cache", "v_cache", "cur_k", "cur_v", "out"):
         setattr(p, name, dummy.data_ptr())
-    p.mask = torch.zeros(4, device="cuda").data_ptr()
+    p.mask = torch.zeros(64, device="cuda").data_ptr()
     p.kv_seq_len = lens.data_ptr()
     p.cur_head_mul = 1
-    p.B, p.H, p.Hkv, p.Q, p.D, p.ctx = B, H, H, 1, 64, 64
+    p.B, p.H, p.Hkv, p.Q, p.D, p.ctx = B, H, H, 4, 128, 64
     p.dtype = p.out_dtype = _lib.DTYPE_F16
     p.sm_scale = 1.0
     p.with_tree = 1
     p.split_mode = _lib.SPLIT_BALANCED
+    p.grid_override = 4000  # 2 * 4000 * 16 rows * 129 floats = 66 MB of partial slots
     for f in ("q_sb", "q_sh", "q_sq", "k_sb", "k_sh", "k_st", "v_sb", "v_sh", "v_st", "ck_sb", "ck_sh", "ck_st",
               "cv_sb", "cv_sh", "cv_st", "o_sb", "o_sh", "o_sq"):
-        setattr(p, f, 64)
+        setattr(p, f, 128)
     assert lib.fta_decode_static(C.byref(p), None) == _lib.FTA_E_TOO_LARGE
