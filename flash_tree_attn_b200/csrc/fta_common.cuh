@@ -84,21 +84,23 @@ struct FtaBalanced {
   }
 
   // Piece of block c that starts at line position lin (lin in c's range).  Returns the
-  // line position where the piece ends.
-  __host__ __device__ long long segment_at(int c, long long lin, FtaSeg& s) const {
-    const long long cbeg = (long long)c * per;
-    long long cend = cbeg + per;
-    if (cend > total) cend = total;
-    const int b = find_b(lin);
+  // line position where the piece ends.  I is the integer type of line positions: 32-bit
+  // arithmetic when the whole line fits (64-bit division is slow on the device).
+  template <typename I>
+  __host__ __device__ long long segment_at_t(int c, I lin, FtaSeg& s) const {
+    const I cbeg = (I)c * (I)per;
+    I cend = cbeg + (I)per;
+    if (cend > (I)total) cend = (I)total;
+    const int b = find_b((long long)lin);
     const int ut = pre[b + 1] - pre[b];
-    const long long boff = lin - (long long)U * pre[b];
-    const int j = (int)(boff / ut);
-    const int t0 = (int)(boff - (long long)j * ut);
-    const long long ustart = lin - t0, uend = ustart + ut;
-    const long long send = cend < uend ? cend : uend;
+    const I boff = lin - (I)U * (I)pre[b];
+    const int j = (int)(boff / (I)ut);
+    const int t0 = (int)(boff - (I)j * (I)ut);
+    const I ustart = lin - (I)t0, uend = ustart + (I)ut;
+    const I send = cend < uend ? cend : uend;
     const int t1 = t0 + (int)(send - lin);
     const int nb = ut - n_tree;  // cache tiles of this unit
-    const int cfirst = (int)(ustart / per), clast = (int)((uend - 1) / per);
+    const int cfirst = (int)(ustart / (I)per), clast = (int)((uend - 1) / (I)per);
     s.b = b;
     s.j = j;
     s.c0 = (t0 < nb ? t0 : nb) * FTA_TILE;
@@ -108,8 +110,13 @@ struct FtaBalanced {
     s.split = c - cfirst;
     s.nsplit = clast - cfirst + 1;
     s.slot = 2 * c + (lin == cbeg ? 0 : 1);
-    s.p0slot = 2 * cfirst + (ustart == (long long)cfirst * per ? 0 : 1);
-    return send;
+    s.p0slot = 2 * cfirst + (ustart == (I)cfirst * (I)per ? 0 : 1);
+    return (long long)send;
+  }
+  __host__ __device__ long long segment_at(int c, long long lin, FtaSeg& s) const {
+    // positions up to total + per appear in the arithmetic
+    if (total + per < 0x7fffffffLL) return segment_at_t<unsigned int>(c, (unsigned int)lin, s);
+    return segment_at_t<long long>(c, lin, s);
   }
 
   // For the merge: pieces of unit (b, j) and the slot of piece i.

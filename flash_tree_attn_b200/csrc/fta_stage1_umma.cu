@@ -159,6 +159,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef FTA_UMMA_PROFILE
   const long long prof_t0 = clock64();
+  if (blockIdx.x == 0 && threadIdx.x == 0) g_umma_trace_t0 = prof_t0;
   unsigned long long prof_g0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #endif
@@ -188,9 +189,15 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     *abort_flag = 0;
     fence_barrier_init();
   }
-  // Q rows the TMA box never covers (M tile padding) must read as zero
-  for (uint32_t i = tid; i < kQBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sm + OFF_Q)[i] = make_uint4(0, 0, 0, 0);
-  fence_proxy_async();
+  // Q rows the TMA box never covers (M tile padding) must read as zero; the epilogue, which
+  // borrows the buffer, leaves them alone too.
+  {
+    const uint32_t box_rows = (uint32_t)(g.qpt * g.hpt);
+    for (uint32_t i = tid; i < kQBytes / 16; i += kThreads) {
+      const uint32_t r = (i >> 3) & (kR - 1);  // [half][row][8 chunks]
+      if ((r & (kR / CS - 1)) >= box_rows) reinterpret_cast<uint4*>(sm + OFF_Q)[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
   if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, pre);
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
@@ -238,6 +245,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
             ok = mbar_wait(BAR((which == 0 ? B_KEMPTY : B_VEMPTY) + st), ((t / NS) & 1) ^ 1, abort_flag, 0x102 + which);
             if (!ok) break;
             const uint32_t dst = base + OFF_RING + st * kStage + (which == 0 ? 0u : kKBytes);
+            FTA_TRACE(t, which);
             mbar_expect_tx(full, kKBytes);
             tma_load_4d(dst, m, full, 0, row0, head, seg.b);
             tma_load_4d(dst + kKVHalf, m, full, 64, row0, head, seg.b);
@@ -275,6 +283,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         if (!ok) break;
         tc_fence_after();
         if (elect_one()) {
+          FTA_TRACE(t, 2);
           const uint64_t dK = dK0 + (uint64_t)((st * kStage) >> 4);
           const uint32_t d_tmem = tmem + kColS + FTA_TILE * sbuf;
 #pragma unroll
@@ -309,8 +318,10 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
         ok = wait_all(BAR(B_PREADY + sbuf), (t / kNBuf) & 1, abort_flag, 0x214);  // P(t) is in TMEM
         if (!ok) break;
+        if (lane == 0) FTA_TRACE(t, 6);
         ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x215);
         if (!ok) break;
+        if (lane == 0) FTA_TRACE(t, 7);
         if (i == 0) {  // the previous piece's epilogue must have read O
           ok = wait_all(BAR(B_OFREE), (sidx & 1) ^ 1, abort_flag, 0x216);
           if (!ok) break;
@@ -378,10 +389,11 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(BAR(B_QREADY));
-      mbar_arrive(BAR(B_QEMPTY));
       ++sidx;
       return true;
     };
+    // The Q buffer doubles as the staging area of the epilogue's stores (each warp uses the rows
+    // it read its own Q rows from), so it is handed back to the producer only after those.
     // V rows past the end of the sequence are zeroed so that 0 * padding cannot give NaN
     auto zero_v_tail = [&](uint32_t t, int valid) -> bool {
       const uint32_t st = t % NS;
@@ -400,7 +412,10 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       fta_cut_desc(p, g)[blockIdx.x] = make_int4(0, 0, 0, 0);  // rewritten below if a cut unit opens this block
     FtaSeg seg;
     bool have = w.next(seg);
-    if (have) ok = q_to_tmem();
+    if (have) {
+      ok = q_to_tmem();
+      mbar_arrive(BAR(B_QEMPTY));
+    }
     while (ok && have) {
       const FtaUnit unit = fta_unit(g, seg.j);
       const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
@@ -410,8 +425,10 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       float m_used = -INFINITY, l = 0.f;
       const uint32_t t_last = gt + n - 1;
       const bool working = __any_sync(0xffffffffu, rvalid) != 0;
+      // The piece after this one is looked up now, while the first S tile is still being computed,
+      // instead of between the two pieces.
       FtaSeg nseg;
-      bool nhave;
+      const bool nhave = w.next(nseg);
 
       if (!working) {
         // a warp whose 32 rows are all M-tile padding only keeps the barrier protocol going
@@ -446,15 +463,17 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           ++xcount;
         }
         gt += n;
-        have = w.next(seg);
-        if (have) ok = q_to_tmem();
+        if (nhave) {
+          ok = q_to_tmem();
+          mbar_arrive(BAR(B_QEMPTY));
+        }
+        seg = nseg;
+        have = nhave;
         continue;
       }
 
       for (int i = 0; i < n; ++i) {
         const uint32_t t = gt + i, sbuf = t % kNBuf;
-        ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
-        if (!ok) break;
         const bool is_tree = i >= n_ct;
         int valid, col0 = 0;
         if (!is_tree) {
@@ -464,6 +483,15 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           col0 = (seg.tt0 + i - n_ct) * FTA_TILE;
           valid = p.Q - col0 < FTA_TILE ? p.Q - col0 : FTA_TILE;
         }
+        // a tree tile's mask row is pulled into L1 while S is still being computed
+        if (is_tree && mrow != nullptr) {
+#pragma unroll
+          for (int c = 0; c < NC; c += 32)
+            if (c < valid - cbase) asm volatile("prefetch.global.L1 [%0];" ::"l"(mrow + col0 + cbase + c));
+        }
+        ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
+        if (!ok) break;
+        if (row == 0) FTA_TRACE(t, 3);
         tc_fence_after();
         float s[NC];
 #pragma unroll
@@ -490,10 +518,25 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
           const int vh = valid - cbase;  // valid columns among this thread's
           if (is_tree && mrow != nullptr) {
+            // All loads first, so that they are in flight together; 16-byte loads where the row
+            // allows it (a thread reads a row of its own, so every load costs a pass per lane).
+            float mv[NC];
+            const float* mp = mrow + col0 + cbase;
+            const bool v4 = (reinterpret_cast<uintptr_t>(mp) & 15) == 0;
+#pragma unroll
+            for (int c = 0; c < NC; c += 4) {
+              if (v4 && c + 3 < vh) {
+                const float4 x = __ldg(reinterpret_cast<const float4*>(mp + c));
+                mv[c] = x.x; mv[c + 1] = x.y; mv[c + 2] = x.z; mv[c + 3] = x.w;
+              } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mv[c + k] = c + k < vh ? __ldg(mp + c + k) : 0.f;
+              }
+            }
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
               float v = s[c] * scale2;
-              if (c < vh) v += __ldg(mrow + col0 + cbase + c) * FTA_LOG2E;
+              if (c < vh) v = fmaf(mv[c], FTA_LOG2E, v);
               else v = -INFINITY;
               s[c] = v;
               mx[c & 3] = fmaxf(mx[c & 3], v);
@@ -548,6 +591,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         }
         l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
         // P[t%3] was the A operand of PV(t-3), which completed before S(t) was even issued
+        if (row == 0) FTA_TRACE(t, 4);
         if (CS == 2) tmem_st16(t_lane + kColP + 32 * sbuf + 16 * chalf, pk);
         else tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
         if (!is_tree && valid < FTA_TILE) {
@@ -557,88 +601,191 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(BAR(B_PREADY + sbuf));
+        if (row == 0) FTA_TRACE(t, 5);
       }
       if (!ok) break;
 
       // ---- epilogue of the piece: O row / l, LSE ------------------------------------------
+      if (row == 0) FTA_TRACE_EP(sidx - 1, 0);
       ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x304);
       if (!ok) break;
       tc_fence_after();
-      float o[kD];
-#pragma unroll
-      for (int ch = 0; ch < kD / 32; ++ch) tmem_ld32(t_lane + ch * 32, o + ch * 32);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(BAR(B_OFREE));
-      // hand the next piece's Q to the MMA issuer before spending time on this piece's stores
-      nhave = w.next(nseg);
+      const uint32_t ep_idx = sidx - 1;
+      if (row == 0) FTA_TRACE_EP(ep_idx, 1);
+      // Every MMA of the piece is complete, so the Q columns of TMEM may be rewritten: the next
+      // piece's Q goes in first and its S tiles are computed while this piece's O is stored.
       if (nhave) {
         ok = q_to_tmem();
         if (!ok) break;
       }
+      if (row == 0) FTA_TRACE_EP(ep_idx, 2);
+      float w0 = 1.f, w1 = 0.f;
+      float* xo = reinterpret_cast<float*>(sm + OFF_X);
       if (CS == 2) {
         // The two halves of the tile's rows hold two partial attentions of the same queries (over
         // the lower / upper 32 columns of every tile).  The upper half parks its unnormalised O row,
         // maximum and row sum in shared memory (16-byte chunks XOR-swizzled by row: conflict-free);
-        // the lower half folds them into its own and goes on to store the result.
-        float* xo = reinterpret_cast<float*>(sm + OFF_X);
+        // the lower half folds them into its own while it stores the result.
         float* xm = xo + 64 * 128;
         if (chalf == 1) {
           ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x30a);
           if (!ok) break;
 #pragma unroll
-          for (int j = 0; j < kD / 4; ++j)
-            *reinterpret_cast<float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2)) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          for (int ch = 0; ch < kD / 32; ++ch) {
+            float o[32];
+            tmem_ld32(t_lane + ch * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(xo + lrow * 128 + (((ch * 8 + j) ^ (lrow & 31)) << 2)) =
+                  make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          }
           xm[2 * lrow] = m_used;
           xm[2 * lrow + 1] = l;
+          tc_fence_before();
+          mbar_arrive(BAR(B_OFREE));
           mbar_arrive(BAR(B_XFULL));
         } else {
           ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x30b);
           if (!ok) break;
           const float m1 = xm[2 * lrow], l1 = xm[2 * lrow + 1];
           const float mstar = fmaxf(m_used, m1);
-          const float w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
-          const float w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
-#pragma unroll
-          for (int j = 0; j < kD / 4; ++j) {
-            const float4 v = *reinterpret_cast<const float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2));
-            o[4 * j] = o[4 * j] * w0 + v.x * w1; o[4 * j + 1] = o[4 * j + 1] * w0 + v.y * w1;
-            o[4 * j + 2] = o[4 * j + 2] * w0 + v.z * w1; o[4 * j + 3] = o[4 * j + 3] * w0 + v.w * w1;
-          }
+          w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
+          w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
           l = l * w0 + l1 * w1;
           m_used = mstar;
-          mbar_arrive(BAR(B_XFREE));
         }
         ++xcount;
       }
+      if (row == 0) FTA_TRACE_EP(ep_idx, 3);
 
       if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 1 && row == 0)
         fta_cut_desc(p, g)[blockIdx.x] = make_int4(seg.b, seg.j, seg.nsplit, seg.p0slot);  // for stage 2
-      if (rvalid && chalf == 0) {
+      if (CS == 1 || chalf == 0) {  // uniform per warp: the upper half's warps have nothing to store
+        const bool rstore = rvalid;
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
         const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
         const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
         void* dst;
         int dt = FTA_DTYPE_F32;
-        long long off;
+        long long off = 0;
         if (final_direct) {
-          dst = p.out; dt = p.out_dtype; off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
-          if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
+          dst = p.out; dt = p.out_dtype;
+          if (rstore) {
+            off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
+            if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
+          }
         } else if (p.split_mode == FTA_SPLIT_BALANCED) {
           dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
-          ws_l[(long long)seg.slot * g.R + lrow] = lse;
+          if (rstore) ws_l[(long long)seg.slot * g.R + lrow] = lse;
         } else if (tree_piece) {
-          const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
-          dst = p.tree_o; off = ro * kD;
-          p.tree_lse[ro] = lse;
+          dst = p.tree_o;
+          if (rstore) {
+            const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
+            off = ro * kD;
+            p.tree_lse[ro] = lse;
+          }
         } else {
-          dst = p.mid_o; off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
-          p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+          dst = p.mid_o;
+          if (rstore) {
+            off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
+            p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+          }
         }
+        // O leaves TMEM 32 columns at a time (a thread never holds its whole row) and goes through
+        // the Q buffer, this warp's own 32 rows of it, so that every store instruction of the warp
+        // writes two whole 256-byte row pieces: thread = row on the way in (16-byte chunks
+        // XOR-swizzled by row), 16 lanes per row on the way out.  fp32 rows take two passes of 64
+        // columns, 16-bit rows one pass of 128.
+        const bool wide = dt == FTA_DTYPE_F32 ||
+                          (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((p.o_sb | p.o_sh | p.o_sq) & 7) == 0);
+        uint8_t* stg = sm + OFF_Q;
+        const float f0 = w0 * inv, f1 = w1 * inv;
 #pragma unroll
-        for (int c4 = 0; c4 < kD; c4 += 4)
-          fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
+        for (int ch = 0; ch < kD / 32; ++ch) {
+          float o[32];
+          tmem_ld32(t_lane + ch * 32, o);
+          tmem_ld_wait();
+          if (ch == kD / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(BAR(B_OFREE));
+          }
+          if (CS == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 v = *reinterpret_cast<const float4*>(xo + lrow * 128 + (((ch * 8 + j) ^ (lrow & 31)) << 2));
+              o[4 * j] = o[4 * j] * f0 + v.x * f1; o[4 * j + 1] = o[4 * j + 1] * f0 + v.y * f1;
+              o[4 * j + 2] = o[4 * j + 2] * f0 + v.z * f1; o[4 * j + 3] = o[4 * j + 3] * f0 + v.w * f1;
+            }
+            if (ch == kD / 32 - 1) mbar_arrive(BAR(B_XFREE));
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] *= inv;
+          }
+          if (!wide) {
+            if (rstore) {
+#pragma unroll
+              for (int c4 = 0; c4 < 32; c4 += 4)
+                fta_store4(dst, dt, off + ch * 32 + c4, make_float4(o[c4], o[c4 + 1], o[c4 + 2], o[c4 + 3]));
+            }
+            continue;
+          }
+          if (dt == FTA_DTYPE_F32) {
+            if ((ch & 1) == 0) __syncwarp();  // the previous pass has been read out
+            if (rstore) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(stg + (ch & 1) * kQHalf + row * 128 + ((j ^ (row & 7)) << 4)) =
+                    make_uint4(__float_as_uint(o[4 * j]), __float_as_uint(o[4 * j + 1]), __float_as_uint(o[4 * j + 2]),
+                               __float_as_uint(o[4 * j + 3]));
+            }
+          } else {
+            if (rstore) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                if (dt == FTA_DTYPE_F16) {
+                  v.x = FtaType<__half>::pack(o[8 * j], o[8 * j + 1]); v.y = FtaType<__half>::pack(o[8 * j + 2], o[8 * j + 3]);
+                  v.z = FtaType<__half>::pack(o[8 * j + 4], o[8 * j + 5]); v.w = FtaType<__half>::pack(o[8 * j + 6], o[8 * j + 7]);
+                } else {
+                  v.x = FtaType<__nv_bfloat16>::pack(o[8 * j], o[8 * j + 1]); v.y = FtaType<__nv_bfloat16>::pack(o[8 * j + 2], o[8 * j + 3]);
+                  v.z = FtaType<__nv_bfloat16>::pack(o[8 * j + 4], o[8 * j + 5]); v.w = FtaType<__nv_bfloat16>::pack(o[8 * j + 6], o[8 * j + 7]);
+                }
+                const int c = (ch & 1) * 4 + j;
+                *reinterpret_cast<uint4*>(stg + (ch >> 1) * kQHalf + row * 128 + ((c ^ (row & 7)) << 4)) = v;
+              }
+            }
+          }
+          const bool flush = dt == FTA_DTYPE_F32 ? (ch & 1) == 1 : ch == kD / 32 - 1;
+          if (flush) {
+            const int pass = dt == FTA_DTYPE_F32 ? ch >> 1 : 0;
+            const uint32_t esize = dt == FTA_DTYPE_F32 ? 4u : 2u;
+            __syncwarp();
+            // all shared-memory reads first, then all stores: neither waits for the other
+            const int c = lane & 15;
+            uint4 vals[16];
+#pragma unroll
+            for (int it = 0; it < 16; ++it) {
+              const int rr = quad * 32 + 2 * it + (lane >> 4);
+              vals[it] = *reinterpret_cast<const uint4*>(stg + (c >> 3) * kQHalf + rr * 128 + (((c & 7) ^ (rr & 7)) << 4));
+            }
+            uint8_t* gdst = reinterpret_cast<uint8_t*>(dst) + pass * 256 + c * 16;
+#pragma unroll
+            for (int it = 0; it < 16; ++it) {
+              const int rl = 2 * it + (lane >> 4);
+              const long long roff = __shfl_sync(0xffffffffu, off, rl);
+              const bool rv = __shfl_sync(0xffffffffu, rstore ? 1 : 0, rl) != 0;
+              if (rv) __stcg(reinterpret_cast<uint4*>(gdst + roff * esize), vals[it]);
+            }
+          }
+        }
+        __syncwarp();
+      }
+      if (row == 0) FTA_TRACE_EP(ep_idx, 6);
+      if (nhave) {  // the staging area is the next Q tile's again
+        fence_proxy_async();
+        mbar_arrive(BAR(B_QEMPTY));
       }
       gt += n;
       seg = nseg;
@@ -805,6 +952,9 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
 }
 
 #ifdef FTA_UMMA_PROFILE
+extern "C" int fta_umma_trace(long long* out512) {
+  return cudaMemcpyFromSymbol(out512, g_umma_trace, sizeof(long long) * 640) == cudaSuccess ? 0 : -1;
+}
 extern "C" int fta_umma_prof(unsigned long long* out64) {
   unsigned long long zero[160] = {0};
   if (cudaMemcpyFromSymbol(out64, g_umma_prof, sizeof(zero)) != cudaSuccess) return -1;

@@ -47,8 +47,21 @@ __device__ unsigned long long g_umma_prof[160];
     if (blockIdx.x == 0 && (threadIdx.x & 31) == 0)                                                  \
       atomicAdd(&g_umma_prof[(((code) >> 8) & 3) * 32 + ((code) & 31)], (unsigned long long)(cycles)); \
   } while (0)
+// timeline of the first 64 tiles of block 0: g_umma_trace[tile][event] = cycles since kernel start
+__device__ long long g_umma_trace[80 * 8];  // rows 64..79: epilogue events of the first 16 pieces
+__device__ long long g_umma_trace_t0;
+#define FTA_TRACE(tile, ev)                                                              \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && (tile) < 64u) g_umma_trace[(tile) * 8 + (ev)] = clock64() - g_umma_trace_t0; \
+  } while (0)
+#define FTA_TRACE_EP(piece, ev)                                                          \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && (piece) < 16u) g_umma_trace[(64 + (piece)) * 8 + (ev)] = clock64() - g_umma_trace_t0; \
+  } while (0)
 #else
 #define FTA_PROF_ADD(code, cycles) do {} while (0)
+#define FTA_TRACE(tile, ev) do {} while (0)
+#define FTA_TRACE_EP(piece, ev) do {} while (0)
 #endif
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code) {
