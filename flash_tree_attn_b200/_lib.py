@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfta.so")
+# FTA_LIB_PATH points at a library built elsewhere (same ABI); the default is the in-tree build.
+LIB_PATH = os.environ.get("FTA_LIB_PATH") or os.path.join(_HERE, "libfta.so")
 
 FTA_OK = 0
 FTA_E_BADARG = 1

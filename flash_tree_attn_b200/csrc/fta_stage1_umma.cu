@@ -37,7 +37,9 @@
 
 namespace fta_umma {
 
-constexpr int kThreads = 224;  // warp 0 TMA producer, 1 QK issuer, 2-5 softmax, 6 PV issuer
+constexpr int kThreads = 384;  // warps 0-3: TMA producer, QK issuer, PV issuer, planner; 4-7 softmax; 8-11 epilogue
+// Registers per thread after the warpgroups have rebalanced (the block is launched with 168 each)
+constexpr int kRegsIssue = 64, kRegsSoftmax = 240, kRegsEpilogue = 200;
 constexpr int kD = 128;
 constexpr int kR = 128;
 constexpr uint32_t kQHalf = kR * 128;         // 128 rows x 64 elements
@@ -47,7 +49,9 @@ constexpr uint32_t kKBytes = 2 * kKVHalf;
 constexpr uint32_t kStage = 2 * kKBytes;      // K tile then V tile
 constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_RING = OFF_Q + kQBytes;
-constexpr uint32_t kBarBytes = 448;
+constexpr uint32_t kBarBytes = 512;
+constexpr int kSegRing = 8;                  // pieces of work the planner may run ahead
+constexpr uint32_t kSegBytes = kSegRing * 64;
 // TMEM columns (32-bit): O fp32 | S fp32 x3 | Q 16-bit pairs | P 16-bit pairs x3.  Three S and P
 // buffers let S = Q K^T run three tiles ahead of the softmax and take PV(t-3), not PV(t-2), as the
 // product a new P must not overwrite: neither wait is then ever on the softmax's critical path.
@@ -56,23 +60,24 @@ constexpr int kNBuf = 3;
 constexpr uint32_t kColS = 128;  // + 64 * buffer
 constexpr uint32_t kColQ = 320;  // 64 columns: 128 head-dim elements, two per column
 constexpr uint32_t kColP = 384;  // + 32 * buffer: 64 KV columns, two per column
+constexpr uint32_t kColStat = 480;  // a row's running maximum and sum, handed from the softmax to the epilogue warps
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
 constexpr uint32_t kXBytes = 64 * 128 * 4 + 64 * 2 * 4;  // CS = 2: one unnormalised O half + (m, l) per query row
 constexpr size_t smem_bytes(int ns, int B, int cs) {
-  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + (size_t)(B + 1) * 4 + 1024;
+  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + kSegBytes + (size_t)(B + 1) * 4 + 1024;
 }
 
 // mbarrier slots (ring barriers are sized for the largest ring)
 constexpr int kMaxNS = 6;
 enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
        B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + 3,
-       B_FINAL = B_PREADY + 3, B_XFULL = B_FINAL + 2, B_XFREE, B_COUNT };
+       B_FINAL = B_PREADY + 3, B_XFULL = B_FINAL + 2, B_XFREE, B_SEGFULL, B_SEGFREE = B_SEGFULL + kSegRing,
+       B_STATS = B_SEGFREE + kSegRing, B_STATSFREE, B_COUNT };
 // A parity wait is only meaningful while the barrier is at most one phase ahead of the phase
 // asked for.  PV(t) therefore commits to B_ODONE + (t & 3): whoever has seen S(t') ready knows
 // that PV(t'-4) and everything before it is complete, so for t in [t'-3, t'] the barrier of PV(t)
 // has completed phase (t>>2)-1 and cannot have completed more than phase t>>2.
-constexpr uint32_t kBarArea = 448;
-static_assert(B_COUNT * 8 + 8 <= kBarArea, "barrier area");
+static_assert(B_COUNT * 8 + 8 <= kBarBytes, "barrier area");
 
 struct Maps {
   CUtensorMap q, k, v, ck, cv;
@@ -130,14 +135,31 @@ struct Walker {
   }
 };
 
-// Warp-collective wait: every lane gets the same answer, so the lanes of a softmax warp leave
-// their loops together (the TMEM loads that follow are warp-wide instructions).
+// One piece of work as the planner warp hands it to the other roles (shared memory, 64 bytes).
+struct __align__(16) SegDesc {
+  int valid;            // 0: the block has no more work
+  int b, kvh, gt, qt;   // sequence; KV head, group tile and query tile of the unit
+  int c0, c1;           // cache rows [c0, c1), c1 already clamped to the sequence length
+  int tt0, tt1;         // tree tiles [tt0, tt1)
+  int split, nsplit, slot, p0slot, j;
+  int pad[2];
+};
+static_assert(sizeof(SegDesc) == 64, "descriptor size");
+
+// Warp-collective wait: every lane gets the same answer, so the lanes of a warp leave their loops
+// together (the TMEM loads that follow are warp-wide instructions).
 __device__ __forceinline__ bool wait_all(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code)) != 0;
 }
 
-__device__ __forceinline__ int seg_cache_tiles(const FtaSeg& s) {
+__device__ __forceinline__ int seg_cache_tiles(const SegDesc& s) {
   return s.c1 > s.c0 ? fta_cdiv(s.c1 - s.c0, FTA_TILE) : 0;
+}
+__device__ __forceinline__ void seg_copy(SegDesc& d, const SegDesc* src) {
+  const int4* s4 = reinterpret_cast<const int4*>(src);
+  int4* d4 = reinterpret_cast<int4*>(&d);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) d4[i] = s4[i];
 }
 
 template <typename T, int NS, int CS>
@@ -145,14 +167,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ Maps maps) {
   constexpr uint32_t OFF_X = OFF_RING + NS * kStage;
   constexpr uint32_t OFF_BAR = OFF_X + (CS == 2 ? kXBytes : 0);
-  constexpr uint32_t OFF_PRE = OFF_BAR + kBarBytes;
+  constexpr uint32_t OFF_SEG = OFF_BAR + kBarBytes;
+  constexpr uint32_t OFF_PRE = OFF_SEG + kSegBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzle atoms are 1024-byte aligned
   uint8_t* sm = smem_raw + (base - raw);
   int* pre = reinterpret_cast<int*>(sm + OFF_PRE);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + 440);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + 444);
+  SegDesc* segq = reinterpret_cast<SegDesc*>(sm + OFF_SEG);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_BAR + kBarBytes - 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + kBarBytes - 4);
   const uint32_t bar0 = base + OFF_BAR;
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
 
@@ -166,29 +190,18 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   const int G = p.H / p.Hkv;
   const int fmt = p.dtype == FTA_DTYPE_BF16 ? 1 : 0;
 
-  if (tid == 0) {
-    mbar_init(BAR(B_QFULL), 1);
-    mbar_init(BAR(B_QEMPTY), 128);
-    mbar_init(BAR(B_QREADY), 128);
-    for (int s = 0; s < 4; ++s) mbar_init(BAR(B_ODONE + s), 1);
-    mbar_init(BAR(B_OFREE), 128);
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(BAR(B_KFULL + s), 1);
-      mbar_init(BAR(B_VFULL + s), 1);
-      mbar_init(BAR(B_KEMPTY + s), 1);
-      mbar_init(BAR(B_VEMPTY + s), 1);
-    }
-    for (int s = 0; s < kNBuf; ++s) {
-      mbar_init(BAR(B_SFULL + s), 1);
-      mbar_init(BAR(B_PREADY + s), 128);
-    }
-    mbar_init(BAR(B_FINAL), 1);
-    mbar_init(BAR(B_FINAL + 1), 1);
-    mbar_init(BAR(B_XFULL), 64);
-    mbar_init(BAR(B_XFREE), 64);
-    *abort_flag = 0;
+  // one barrier per thread: slot i expects count(i) arrivals per phase
+  if (tid < B_COUNT) {
+    uint32_t count = 1;
+    if (tid == B_QEMPTY || tid == B_QREADY || tid == B_OFREE || tid == B_STATS || tid == B_STATSFREE ||
+        (tid >= B_PREADY && tid < B_PREADY + kNBuf))
+      count = 128;
+    else if (tid == B_XFULL || tid == B_XFREE) count = 64;
+    else if (tid >= B_SEGFREE && tid < B_SEGFREE + kSegRing) count = 4;
+    mbar_init(BAR(tid), count);
     fence_barrier_init();
   }
+  if (tid == 0) *abort_flag = 0;
   // Q rows the TMA box never covers (M tile padding) must read as zero; the epilogue, which
   // borrows the buffer, leaves them alone too.
   {
@@ -205,148 +218,188 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 0) {
-    // ================================ TMA producer ================================
-    if (lane == 0) {
-      tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
-      if (g.n_tree) { tma_prefetch_desc(&maps.ck); tma_prefetch_desc(&maps.cv); }
-      Walker w(p, g, pre);
-      FtaSeg seg;
-      uint32_t gt = 0, sidx = 0;
-      bool ok = true;
-      while (ok && w.next(seg)) {
-        const FtaUnit unit = fta_unit(g, seg.j);
-        const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
-        const int q_at = n < 2 ? n : 2;
-        // K tiles run two ahead of V tiles, as their consumers (S = Q K^T, O += P V) do.  The
-        // first K tiles of a piece are requested before its Q tile: they do not depend on the
-        // Q buffer of the previous piece having been read, so they overlap its tail.
-        for (int u = 0; u < n + 2 && ok; ++u) {
-          if (u == q_at) {
-            ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
-            if (!ok) break;
-            mbar_expect_tx(BAR(B_QFULL), 2u * CS * (uint32_t)(g.qpt * g.hpt) * 128u);
-            const int h0 = unit.kvh * G + unit.gt * g.hpt, q0 = unit.qt * g.qpt;
+  if (warp < 4) {
+    reg_dec<kRegsIssue>();
+    if (warp == 3) {
+      // ================================ planner =====================================
+      // Walks this block's pieces of work once, for everybody: the lookup (a search in the prefix
+      // table, divisions, a sequence length from global memory) is off every other role's path.
+      if (lane == 0) {
+        Walker w(p, g, pre);
+        FtaSeg seg;
+        for (uint32_t k = 0;; ++k) {
+          const bool have = w.next(seg);
+          const uint32_t slot = k % kSegRing;
+          if (k >= kSegRing && !mbar_wait(BAR(B_SEGFREE + slot), ((k / kSegRing) - 1) & 1, abort_flag, 0x402)) break;
+          SegDesc d;
+          d.valid = have ? 1 : 0;
+          if (have) {
+            const FtaUnit unit = fta_unit(g, seg.j);
+            d.b = seg.b; d.kvh = unit.kvh; d.gt = unit.gt; d.qt = unit.qt;
+            d.c0 = seg.c0; d.c1 = seg.c1; d.tt0 = seg.tt0; d.tt1 = seg.tt1;
+            d.split = seg.split; d.nsplit = seg.nsplit; d.slot = seg.slot; d.p0slot = seg.p0slot; d.j = seg.j;
+          } else {
+            d.b = d.kvh = d.gt = d.qt = d.c0 = d.c1 = d.tt0 = d.tt1 = d.split = d.nsplit = d.slot = d.p0slot = d.j = 0;
+          }
+          d.pad[0] = d.pad[1] = 0;
+          int4* dst = reinterpret_cast<int4*>(&segq[slot]);
+          const int4* src = reinterpret_cast<const int4*>(&d);
 #pragma unroll
-            for (int dup = 0; dup < CS; ++dup) {  // CS = 2: the same rows again at tile rows 64..
-              tma_load_4d(base + OFF_Q + dup * 64 * 128, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
-              tma_load_4d(base + OFF_Q + kQHalf + dup * 64 * 128, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
+          for (int i = 0; i < 4; ++i) dst[i] = src[i];
+          mbar_arrive(BAR(B_SEGFULL + slot));  // release: the descriptor is visible to whoever sees the phase
+          if (!have) break;
+        }
+      }
+    } else if (warp == 0) {
+      // ================================ TMA producer ================================
+      if (lane == 0) {
+        tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
+        if (g.n_tree) { tma_prefetch_desc(&maps.ck); tma_prefetch_desc(&maps.cv); }
+        uint32_t gt = 0;
+        bool ok = true;
+        for (uint32_t sidx = 0; ok; ++sidx) {
+          SegDesc seg;
+          ok = mbar_wait(BAR(B_SEGFULL + sidx % kSegRing), (sidx / kSegRing) & 1, abort_flag, 0x100);
+          if (!ok) break;
+          seg_copy(seg, &segq[sidx % kSegRing]);
+          if (!seg.valid) break;
+          const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
+          const int q_at = n < 2 ? n : 2;
+          // K tiles run two ahead of V tiles, as their consumers (S = Q K^T, O += P V) do.  The
+          // first K tiles of a piece are requested before its Q tile: they do not depend on the
+          // Q buffer having been handed back, so they overlap the previous piece's tail.
+          for (int u = 0; u < n + 2 && ok; ++u) {
+            if (u == q_at) {
+              ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
+              if (!ok) break;
+              mbar_expect_tx(BAR(B_QFULL), 2u * CS * (uint32_t)(g.qpt * g.hpt) * 128u);
+              const int h0 = seg.kvh * G + seg.gt * g.hpt, q0 = seg.qt * g.qpt;
+#pragma unroll
+              for (int dup = 0; dup < CS; ++dup) {  // CS = 2: the same rows again at tile rows 64..
+                tma_load_4d(base + OFF_Q + dup * 64 * 128, &maps.q, BAR(B_QFULL), 0, q0, h0, seg.b);
+                tma_load_4d(base + OFF_Q + kQHalf + dup * 64 * 128, &maps.q, BAR(B_QFULL), 64, q0, h0, seg.b);
+              }
+            }
+            for (int which = 0; which < 2; ++which) {  // 0: K of tile u, 1: V of tile u - 2
+              const int i = which == 0 ? u : u - 2;
+              if (i < 0 || i >= n) continue;
+              const uint32_t t = gt + i, st = t % NS;
+              const CUtensorMap* m;
+              int row0, head;
+              if (i < n_ct) { m = which == 0 ? &maps.k : &maps.v; row0 = seg.c0 + i * FTA_TILE; head = seg.kvh; }
+              else { m = which == 0 ? &maps.ck : &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = seg.kvh * p.cur_head_mul; }
+              const uint32_t full = BAR((which == 0 ? B_KFULL : B_VFULL) + st);
+              ok = mbar_wait(BAR((which == 0 ? B_KEMPTY : B_VEMPTY) + st), ((t / NS) & 1) ^ 1, abort_flag, 0x102 + which);
+              if (!ok) break;
+              const uint32_t dst = base + OFF_RING + st * kStage + (which == 0 ? 0u : kKBytes);
+              FTA_TRACE(t, which);
+              mbar_expect_tx(full, kKBytes);
+              tma_load_5d(dst, m, full, 0, row0, head, 0, seg.b);
             }
           }
-          for (int which = 0; which < 2; ++which) {  // 0: K of tile u, 1: V of tile u - 2
-            const int i = which == 0 ? u : u - 2;
-            if (i < 0 || i >= n) continue;
-            const uint32_t t = gt + i, st = t % NS;
-            const CUtensorMap* m;
-            int row0, head;
-            if (i < n_ct) { m = which == 0 ? &maps.k : &maps.v; row0 = seg.c0 + i * FTA_TILE; head = unit.kvh; }
-            else { m = which == 0 ? &maps.ck : &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = unit.kvh * p.cur_head_mul; }
-            const uint32_t full = BAR((which == 0 ? B_KFULL : B_VFULL) + st);
-            ok = mbar_wait(BAR((which == 0 ? B_KEMPTY : B_VEMPTY) + st), ((t / NS) & 1) ^ 1, abort_flag, 0x102 + which);
+          gt += n;
+        }
+      }
+    } else if (warp == 1) {
+      // ================================ S = Q K^T issuer ============================
+      // The whole warp walks the loop (uniform control flow keeps descriptor arithmetic cheap);
+      // one elected lane issues.  S(t) goes to buffer t%3 as soon as the softmax has finished
+      // reading S(t-3), so the products run up to three tiles ahead of the softmax.
+      const uint32_t idesc_qk = instr_desc_f16(fmt, kR, FTA_TILE, 0, 0);
+      const uint64_t dK0 = smem_desc_sw128(base + OFF_RING, 16, 1024);
+      uint32_t gt = 0;
+      bool ok = true;
+      for (uint32_t sidx = 0; ok; ++sidx) {
+        SegDesc seg;
+        ok = wait_all(BAR(B_SEGFULL + sidx % kSegRing), (sidx / kSegRing) & 1, abort_flag, 0x200);
+        if (!ok) break;
+        seg_copy(seg, &segq[sidx % kSegRing]);
+        if (!seg.valid) break;
+        const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
+        ok = wait_all(BAR(B_QREADY), sidx & 1, abort_flag, 0x201);  // Q rows are in TMEM
+        if (lane == 0 && sidx > 0) FTA_TRACE_EP(sidx - 1, 5);
+        for (int i = 0; i < n && ok; ++i) {
+          const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
+          if (t >= kNBuf) {
+            // S[t%3] has been read by softmax(t-3); and PV(t-3) is complete, so that whoever sees
+            // S(t) ready may overwrite P[t%3] without asking.  Both happened about two tiles ago.
+            ok = wait_all(BAR(B_PREADY + sbuf), ((t - kNBuf) / kNBuf) & 1, abort_flag, 0x204);
             if (!ok) break;
-            const uint32_t dst = base + OFF_RING + st * kStage + (which == 0 ? 0u : kKBytes);
-            FTA_TRACE(t, which);
-            mbar_expect_tx(full, kKBytes);
-            tma_load_4d(dst, m, full, 0, row0, head, seg.b);
-            tma_load_4d(dst + kKVHalf, m, full, 64, row0, head, seg.b);
+            ok = wait_all(BAR(B_ODONE + ((t - kNBuf) & 3)), ((t - kNBuf) >> 2) & 1, abort_flag, 0x207);
+            if (!ok) break;
           }
+          ok = wait_all(BAR(B_KFULL + st), (t / NS) & 1, abort_flag, 0x202);
+          if (!ok) break;
+          if (lane == 0 && sidx > 0 && i == 0) FTA_TRACE_EP(sidx - 1, 7);
+          tc_fence_after();
+          if (elect_one()) {
+            FTA_TRACE(t, 2);
+            const uint64_t dK = dK0 + (uint64_t)((st * kStage) >> 4);
+            const uint32_t d_tmem = tmem + kColS + FTA_TILE * sbuf;
+#pragma unroll
+            for (int ks = 0; ks < kD / 16; ++ks) {
+              const uint32_t half = ks >> 2, off = (ks & 3) * 32;
+              umma_f16_ts(d_tmem, tmem + kColQ + ks * 8, dK + (uint64_t)((half * kKVHalf + off) >> 4), idesc_qk, ks > 0);
+            }
+            umma_commit(BAR(B_KEMPTY + st));
+            umma_commit(BAR(B_SFULL + sbuf));
+          }
+          __syncwarp();
         }
         gt += n;
-        ++sidx;
       }
-    }
-  } else if (warp == 1) {
-    // ================================ S = Q K^T issuer ============================
-    // The whole warp walks the loop (uniform control flow keeps descriptor arithmetic cheap);
-    // one elected lane issues.  S(t) goes to buffer t&1 as soon as the softmax has finished
-    // reading S(t-2), so the products run up to two tiles ahead of the softmax.
-    const uint32_t idesc_qk = instr_desc_f16(fmt, kR, FTA_TILE, 0, 0);
-    const uint64_t dK0 = smem_desc_sw128(base + OFF_RING, 16, 1024);
-    Walker w(p, g, pre);
-    FtaSeg seg;
-    uint32_t gt = 0, sidx = 0;
-    bool ok = true;
-    while (ok && w.next(seg)) {
-      const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
-      ok = wait_all(BAR(B_QREADY), sidx & 1, abort_flag, 0x201);  // Q rows are in TMEM
-      for (int i = 0; i < n && ok; ++i) {
-        const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
-        if (t >= kNBuf) {
-          // S[t%3] has been read by softmax(t-3); and PV(t-3) is complete, so that whoever sees
-          // S(t) ready may overwrite P[t%3] without asking.  Both happened about two tiles ago.
-          ok = wait_all(BAR(B_PREADY + sbuf), ((t - kNBuf) / kNBuf) & 1, abort_flag, 0x204);
-          if (!ok) break;
-          ok = wait_all(BAR(B_ODONE + ((t - kNBuf) & 3)), ((t - kNBuf) >> 2) & 1, abort_flag, 0x207);
-          if (!ok) break;
-        }
-        ok = wait_all(BAR(B_KFULL + st), (t / NS) & 1, abort_flag, 0x202);
+      // nothing of this warp's may still be running on the tensor pipe when TMEM is freed
+      if (elect_one()) umma_commit(BAR(B_FINAL));
+      __syncwarp();
+      int zero = 0;
+      mbar_wait(BAR(B_FINAL), 0, &zero, 0x20f);
+    } else {
+      // ================================ O += P V issuer =============================
+      const uint32_t idesc_pv = instr_desc_f16(fmt, kR, kD, 0, 1);
+      const uint64_t dV0 = smem_desc_sw128(base + OFF_RING + kKBytes, kKVHalf, 1024);
+      uint32_t gt = 0;
+      bool ok = true;
+      for (uint32_t sidx = 0; ok; ++sidx) {
+        SegDesc seg;
+        ok = wait_all(BAR(B_SEGFULL + sidx % kSegRing), (sidx / kSegRing) & 1, abort_flag, 0x210);
         if (!ok) break;
-        tc_fence_after();
-        if (elect_one()) {
-          FTA_TRACE(t, 2);
-          const uint64_t dK = dK0 + (uint64_t)((st * kStage) >> 4);
-          const uint32_t d_tmem = tmem + kColS + FTA_TILE * sbuf;
-#pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks) {
-            const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-            umma_f16_ts(d_tmem, tmem + kColQ + ks * 8, dK + (uint64_t)((half * kKVHalf + off) >> 4), idesc_qk, ks > 0);
+        seg_copy(seg, &segq[sidx % kSegRing]);
+        if (!seg.valid) break;
+        const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
+        for (int i = 0; i < n && ok; ++i) {
+          const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
+          ok = wait_all(BAR(B_PREADY + sbuf), (t / kNBuf) & 1, abort_flag, 0x214);  // P(t) is in TMEM
+          if (!ok) break;
+          if (lane == 0) FTA_TRACE(t, 6);
+          ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x215);
+          if (!ok) break;
+          if (lane == 0) FTA_TRACE(t, 7);
+          if (i == 0) {  // the previous piece's epilogue must have read O
+            ok = wait_all(BAR(B_OFREE), (sidx & 1) ^ 1, abort_flag, 0x216);
+            if (!ok) break;
           }
-          umma_commit(BAR(B_KEMPTY + st));
-          umma_commit(BAR(B_SFULL + sbuf));
-        }
-        __syncwarp();
-      }
-      gt += n;
-      ++sidx;
-    }
-    // nothing of this warp's may still be running on the tensor pipe when TMEM is freed
-    if (elect_one()) umma_commit(BAR(B_FINAL));
-    __syncwarp();
-    int zero = 0;
-    mbar_wait(BAR(B_FINAL), 0, &zero, 0x20f);
-  } else if (warp == 6) {
-    // ================================ O += P V issuer =============================
-    const uint32_t idesc_pv = instr_desc_f16(fmt, kR, kD, 0, 1);
-    const uint64_t dV0 = smem_desc_sw128(base + OFF_RING + kKBytes, kKVHalf, 1024);
-    Walker w(p, g, pre);
-    FtaSeg seg;
-    uint32_t gt = 0, sidx = 0;
-    bool ok = true;
-    while (ok && w.next(seg)) {
-      const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
-      for (int i = 0; i < n && ok; ++i) {
-        const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
-        ok = wait_all(BAR(B_PREADY + sbuf), (t / kNBuf) & 1, abort_flag, 0x214);  // P(t) is in TMEM
-        if (!ok) break;
-        if (lane == 0) FTA_TRACE(t, 6);
-        ok = wait_all(BAR(B_VFULL + st), (t / NS) & 1, abort_flag, 0x215);
-        if (!ok) break;
-        if (lane == 0) FTA_TRACE(t, 7);
-        if (i == 0) {  // the previous piece's epilogue must have read O
-          ok = wait_all(BAR(B_OFREE), (sidx & 1) ^ 1, abort_flag, 0x216);
-          if (!ok) break;
-        }
-        tc_fence_after();
-        if (elect_one()) {
-          const uint64_t dV = dV0 + (uint64_t)((st * kStage) >> 4);
+          tc_fence_after();
+          if (elect_one()) {
+            const uint64_t dV = dV0 + (uint64_t)((st * kStage) >> 4);
 #pragma unroll
-          for (int kk = 0; kk < FTA_TILE / 16; ++kk)
-            umma_f16_ts(tmem, tmem + kColP + 32 * sbuf + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
-                        (i > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(BAR(B_VEMPTY + st));
-          umma_commit(BAR(B_ODONE + (t & 3)));
+            for (int kk = 0; kk < FTA_TILE / 16; ++kk)
+              umma_f16_ts(tmem, tmem + kColP + 32 * sbuf + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
+                          (i > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(BAR(B_VEMPTY + st));
+            umma_commit(BAR(B_ODONE + (t & 3)));
+          }
+          __syncwarp();
         }
-        __syncwarp();
+        gt += n;
       }
-      gt += n;
-      ++sidx;
+      if (elect_one()) umma_commit(BAR(B_FINAL + 1));
+      __syncwarp();
+      int zero = 0;
+      mbar_wait(BAR(B_FINAL + 1), 0, &zero, 0x21f);
     }
-    if (elect_one()) umma_commit(BAR(B_FINAL + 1));
-    __syncwarp();
-    int zero = 0;
-    mbar_wait(BAR(B_FINAL + 1), 0, &zero, 0x21f);
-  } else if (warp >= 2 && warp < 6) {
-    // ================================ softmax / epilogue ===========================
+  } else if (warp < 8) {
+    // ================================ softmax =======================================
+    reg_inc<kRegsSoftmax>();
     const int quad = warp & 3;  // the TMEM lane quadrant a warp may touch is fixed by its index
     const int row = quad * 32 + lane;
     constexpr int NC = FTA_TILE / CS;            // KV columns of a tile this thread works on
@@ -354,7 +407,6 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     const int chalf = CS == 2 ? (row >> 6) : 0;  // which NC columns of each tile
     const int cbase = NC * chalf;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
-    uint32_t xcount = 0;  // CS = 2: pieces whose halves have been exchanged so far
     if (CS == 2) {
       // the half of every P row this thread never writes must read as zero
       uint32_t z[16];
@@ -366,16 +418,13 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       tc_fence_before();
     }
     const float scale2 = p.sm_scale * FTA_LOG2E;
-    float* ws_o = reinterpret_cast<float*>(p.workspace);
-    float* ws_l = ws_o + (long long)2 * g.grid * g.R * kD;
-    Walker w(p, g, pre);
     uint32_t gt = 0, sidx = 0;
     bool ok = true;
 
     // Q row of this thread: shared memory (TMA, swizzled) -> TMEM, 16-bit pairs, one per column.
-    // All MMAs of the previous piece are complete when this runs (its O has been read).
-    auto q_to_tmem = [&]() -> bool {
-      if (!wait_all(BAR(B_QFULL), sidx & 1, abort_flag, 0x306)) return false;
+    // Every S = Q K^T of the previous piece is complete when this runs (its last S has been read).
+    auto q_to_tmem = [&](uint32_t piece) -> bool {
+      if (!wait_all(BAR(B_QFULL), piece & 1, abort_flag, 0x306)) return false;
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t qr[32];
@@ -389,11 +438,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(BAR(B_QREADY));
-      ++sidx;
       return true;
     };
-    // The Q buffer doubles as the staging area of the epilogue's stores (each warp uses the rows
-    // it read its own Q rows from), so it is handed back to the producer only after those.
     // V rows past the end of the sequence are zeroed so that 0 * padding cannot give NaN
     auto zero_v_tail = [&](uint32_t t, int valid) -> bool {
       const uint32_t st = t % NS;
@@ -408,27 +454,23 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       return true;
     };
 
-    if (p.split_mode == FTA_SPLIT_BALANCED && row == 0)
-      fta_cut_desc(p, g)[blockIdx.x] = make_int4(0, 0, 0, 0);  // rewritten below if a cut unit opens this block
-    FtaSeg seg;
-    bool have = w.next(seg);
-    if (have) {
-      ok = q_to_tmem();
-      mbar_arrive(BAR(B_QEMPTY));
+    SegDesc seg;
+    ok = wait_all(BAR(B_SEGFULL), 0, abort_flag, 0x300);
+    if (ok) {
+      seg_copy(seg, &segq[0]);
+      if (seg.valid) ok = q_to_tmem(0);
+    } else {
+      seg.valid = 0;
     }
-    while (ok && have) {
-      const FtaUnit unit = fta_unit(g, seg.j);
+    while (ok && seg.valid) {
+      FtaUnit unit;
+      unit.kvh = seg.kvh; unit.gt = seg.gt; unit.qt = seg.qt;
       const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
       int h, qi;
       const bool rvalid = fta_row(p, g, unit, lrow, h, qi);
       const float* mrow = (rvalid && g.n_tree) ? p.mask + seg.b * p.m_sb + h * p.m_sh + qi * p.m_sq : nullptr;
       float m_used = -INFINITY, l = 0.f;
-      const uint32_t t_last = gt + n - 1;
       const bool working = __any_sync(0xffffffffu, rvalid) != 0;
-      // The piece after this one is looked up now, while the first S tile is still being computed,
-      // instead of between the two pieces.
-      FtaSeg nseg;
-      const bool nhave = w.next(nseg);
 
       if (!working) {
         // a warp whose 32 rows are all M-tile padding only keeps the barrier protocol going
@@ -447,9 +489,218 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           mbar_arrive(BAR(B_PREADY + sbuf));
         }
         if (!ok) break;
-        ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x314);
+      } else {
+        for (int i = 0; i < n; ++i) {
+          const uint32_t t = gt + i, sbuf = t % kNBuf;
+          const bool is_tree = i >= n_ct;
+          int valid, col0 = 0;
+          if (!is_tree) {
+            const int row0 = seg.c0 + i * FTA_TILE;
+            valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
+          } else {
+            col0 = (seg.tt0 + i - n_ct) * FTA_TILE;
+            valid = p.Q - col0 < FTA_TILE ? p.Q - col0 : FTA_TILE;
+          }
+          // a tree tile's mask row is pulled into L1 while S is still being computed
+          if (is_tree && mrow != nullptr) {
+#pragma unroll
+            for (int c = 0; c < NC; c += 32)
+              if (c < valid - cbase) asm volatile("prefetch.global.L1 [%0];" ::"l"(mrow + col0 + cbase + c));
+          }
+          ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
+          if (!ok) break;
+          if (row == 0) FTA_TRACE(t, 3);
+          tc_fence_after();
+          float s[NC];
+#pragma unroll
+          for (int k = 0; k < NC / 32; ++k) tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + cbase + 32 * k, s + 32 * k);
+          tmem_ld_wait();
+
+          // Row maximum in the log2 domain (mt) and the factor `mul` that takes s[] there.
+          // Full cache tiles keep the raw scores and fold the scale into the exponent's FMA;
+          // the tree tile and the last, partial tile of a sequence take the general path.
+          float mt, mul;
+          if (!is_tree && valid == FTA_TILE && scale2 > 0.f) {
+            float mx[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) mx[c] = fmax3(s[c], s[c + 8], s[c + 16]);
+#pragma unroll
+            for (int c = 24; c + 8 < NC; c += 16)
+#pragma unroll
+              for (int k = 0; k < 8; ++k) mx[k] = fmax3(mx[k], s[c + k], s[c + 8 + k]);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], s[NC - 8 + c]);
+            mt = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
+            mul = scale2;
+          } else {
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            const int vh = valid - cbase;  // valid columns among this thread's
+            if (is_tree && mrow != nullptr) {
+              // All loads first, so that they are in flight together; 16-byte loads where the row
+              // allows it (a thread reads a row of its own, so every load costs a pass per lane).
+              float mv[NC];
+              const float* mp = mrow + col0 + cbase;
+              const bool v4 = (reinterpret_cast<uintptr_t>(mp) & 15) == 0;
+#pragma unroll
+              for (int c = 0; c < NC; c += 4) {
+                if (v4 && c + 3 < vh) {
+                  const float4 x = __ldg(reinterpret_cast<const float4*>(mp + c));
+                  mv[c] = x.x; mv[c + 1] = x.y; mv[c + 2] = x.z; mv[c + 3] = x.w;
+                } else {
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) mv[c + k] = c + k < vh ? __ldg(mp + c + k) : 0.f;
+                }
+              }
+#pragma unroll
+              for (int c = 0; c < NC; ++c) {
+                float v = s[c] * scale2;
+                if (c < vh) v = fmaf(mv[c], FTA_LOG2E, v);
+                else v = -INFINITY;
+                s[c] = v;
+                mx[c & 3] = fmaxf(mx[c & 3], v);
+              }
+            } else {
+#pragma unroll
+              for (int c = 0; c < NC; ++c) {
+                const float v = c < vh ? s[c] * scale2 : -INFINITY;
+                s[c] = v;
+                mx[c & 3] = fmaxf(mx[c & 3], v);
+              }
+            }
+            mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            mul = 1.f;
+          }
+          // lazy rescale: keep the running max until it is exceeded by more than 2^8; O may only be
+          // touched once the previous PV has finished
+          const bool need = mt > m_used + 8.f;
+          if (i > 0 && __any_sync(0xffffffffu, need)) {
+            ok = wait_all(BAR(B_ODONE + ((t - 1) & 3)), ((t - 1) >> 2) & 1, abort_flag, 0x302);
+            if (!ok) break;
+            tc_fence_after();
+            const float alpha = need ? fta_exp2(m_used - mt) : 1.f;
+#pragma unroll
+            for (int ch = 0; ch < kD / 32; ++ch) {
+              float o[32];
+              tmem_ld32(t_lane + ch * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int k = 0; k < 32; ++k) o[k] *= alpha;
+              tmem_st32(t_lane + ch * 32, o);
+            }
+            tmem_st_wait();
+          }
+          if (need) {
+            l *= fta_exp2(m_used - mt);
+            m_used = mt;
+          }
+          const float nsub = m_used == -INFINITY ? 0.f : -m_used;
+          float ps[4] = {0.f, 0.f, 0.f, 0.f};
+          uint32_t pk[NC / 2];
+#pragma unroll
+          for (int c2 = 0; c2 < NC / 2; ++c2) {
+            const float2 e = ffma2(make_float2(s[2 * c2], s[2 * c2 + 1]), make_float2(mul, mul), make_float2(nsub, nsub));
+            // every other pair is exponentiated on the FMA pipe, so that the MUFU (4 lanes per
+            // clock) and the FMA pipe work side by side
+            float p0, p1;
+            if (c2 & 1) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
+            else { p0 = fta_exp2(e.x); p1 = fta_exp2(e.y); }
+            ps[c2 & 3] += p0 + p1;
+            pk[c2] = FtaType<T>::pack(p0, p1);
+          }
+          l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+          // P[t%3] was the A operand of PV(t-3), which completed before S(t) was even issued
+          if (row == 0) FTA_TRACE(t, 4);
+          if (CS == 2) tmem_st16(t_lane + kColP + 32 * sbuf + 16 * chalf, pk);
+          else tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
+          if (!is_tree && valid < FTA_TILE) {
+            ok = zero_v_tail(t, valid);
+            if (!ok) break;
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(BAR(B_PREADY + sbuf));
+          if (row == 0) FTA_TRACE(t, 5);
+        }
         if (!ok) break;
+      }
+
+      // ---- end of the piece: the row's maximum and sum go to the epilogue warps through two
+      // TMEM columns, and the next piece starts at once --------------------------------------
+      if (row == 0) FTA_TRACE_EP(sidx, 0);
+      ok = wait_all(BAR(B_STATSFREE), (sidx & 1) ^ 1, abort_flag, 0x307);
+      if (!ok) break;
+      tmem_st2(t_lane + kColStat, m_used, l);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(BAR(B_STATS));
+      gt += n;
+      ++sidx;
+      ok = wait_all(BAR(B_SEGFULL + sidx % kSegRing), (sidx / kSegRing) & 1, abort_flag, 0x300);
+      if (!ok) break;
+      seg_copy(seg, &segq[sidx % kSegRing]);
+      if (row == 0) FTA_TRACE_EP(sidx - 1, 1);
+      if (seg.valid) ok = q_to_tmem(sidx);
+      if (row == 0) FTA_TRACE_EP(sidx - 1, 2);
+    }
+  } else {
+    // ================================ epilogue =======================================
+    // O row / l and the LSE of every piece, while the softmax warps are already at work on the
+    // next one.  Same row-to-thread mapping as the softmax warps (TMEM lane quadrant = warp & 3).
+    reg_inc<kRegsEpilogue>();
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int lrow = CS == 2 ? (row & 63) : row;
+    const int chalf = CS == 2 ? (row >> 6) : 0;
+    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+    float* ws_o = reinterpret_cast<float*>(p.workspace);
+    float* ws_l = ws_o + (long long)2 * g.grid * g.R * kD;
+    uint32_t gt = 0, sidx = 0, xcount = 0;
+    bool ok = true;
+
+    if (p.split_mode == FTA_SPLIT_BALANCED && row == 0)
+      fta_cut_desc(p, g)[blockIdx.x] = make_int4(0, 0, 0, 0);  // rewritten below if a cut unit opens this block
+    SegDesc seg, nseg;
+    ok = wait_all(BAR(B_SEGFULL), 0, abort_flag, 0x500);
+    if (ok) seg_copy(seg, &segq[0]);
+    else seg.valid = 0;
+    if (ok && seg.valid) {
+      // the Q buffer goes back to the producer, for the second piece's Q, once the first is in TMEM
+      ok = wait_all(BAR(B_QREADY), 0, abort_flag, 0x501);
+      if (ok) mbar_arrive(BAR(B_QEMPTY));
+    }
+    while (ok && seg.valid) {
+      FtaUnit unit;
+      unit.kvh = seg.kvh; unit.gt = seg.gt; unit.qt = seg.qt;
+      const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
+      const uint32_t t_last = gt + n - 1;
+      int h, qi;
+      const bool rvalid = fta_row(p, g, unit, lrow, h, qi);
+      const bool working = __any_sync(0xffffffffu, rvalid) != 0;
+      ok = wait_all(BAR(B_SEGFULL + (sidx + 1) % kSegRing), ((sidx + 1) / kSegRing) & 1, abort_flag, 0x500);
+      if (!ok) break;
+      seg_copy(nseg, &segq[(sidx + 1) % kSegRing]);
+
+      // the row's maximum and sum, as the softmax thread of the same row left them
+      ok = wait_all(BAR(B_STATS), sidx & 1, abort_flag, 0x502);
+      if (!ok) break;
+      tc_fence_after();
+      float m_used, l;
+      tmem_ld2(t_lane + kColStat, m_used, l);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(BAR(B_STATSFREE));
+
+      ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x304);
+      if (!ok) break;
+      tc_fence_after();
+      if (row == 0) FTA_TRACE_EP(sidx, 3);
+
+      if (!working) {
         mbar_arrive(BAR(B_OFREE));
+        if (nseg.valid) {
+          ok = wait_all(BAR(B_QREADY), (sidx + 1) & 1, abort_flag, 0x503);
+          if (!ok) break;
+        }
         if (CS == 2) {  // keep the halves' exchange barriers in step
           if (chalf == 1) {
             ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x315);
@@ -462,334 +713,162 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           }
           ++xcount;
         }
-        gt += n;
-        if (nhave) {
-          ok = q_to_tmem();
-          mbar_arrive(BAR(B_QEMPTY));
-        }
-        seg = nseg;
-        have = nhave;
-        continue;
-      }
-
-      for (int i = 0; i < n; ++i) {
-        const uint32_t t = gt + i, sbuf = t % kNBuf;
-        const bool is_tree = i >= n_ct;
-        int valid, col0 = 0;
-        if (!is_tree) {
-          const int row0 = seg.c0 + i * FTA_TILE;
-          valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
-        } else {
-          col0 = (seg.tt0 + i - n_ct) * FTA_TILE;
-          valid = p.Q - col0 < FTA_TILE ? p.Q - col0 : FTA_TILE;
-        }
-        // a tree tile's mask row is pulled into L1 while S is still being computed
-        if (is_tree && mrow != nullptr) {
+      } else {
+        // The whole O row goes to registers at once and the accumulator is handed back: the first
+        // O += P V of the next piece is waiting for exactly this.
+        float o[kD];
 #pragma unroll
-          for (int c = 0; c < NC; c += 32)
-            if (c < valid - cbase) asm volatile("prefetch.global.L1 [%0];" ::"l"(mrow + col0 + cbase + c));
-        }
-        ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
-        if (!ok) break;
-        if (row == 0) FTA_TRACE(t, 3);
-        tc_fence_after();
-        float s[NC];
-#pragma unroll
-        for (int k = 0; k < NC / 32; ++k) tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + cbase + 32 * k, s + 32 * k);
+        for (int ch = 0; ch < kD / 32; ++ch) tmem_ld32(t_lane + ch * 32, o + ch * 32);
         tmem_ld_wait();
-
-        // Row maximum in the log2 domain (mt) and the factor `mul` that takes s[] there.
-        // Full cache tiles keep the raw scores and fold the scale into the exponent's FMA;
-        // the tree tile and the last, partial tile of a sequence take the general path.
-        float mt, mul;
-        if (!is_tree && valid == FTA_TILE && scale2 > 0.f) {
-          float mx[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) mx[c] = fmax3(s[c], s[c + 8], s[c + 16]);
-#pragma unroll
-          for (int c = 24; c + 8 < NC; c += 16)
-#pragma unroll
-            for (int k = 0; k < 8; ++k) mx[k] = fmax3(mx[k], s[c + k], s[c + 8 + k]);
-#pragma unroll
-          for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], s[NC - 8 + c]);
-          mt = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
-          mul = scale2;
-        } else {
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-          const int vh = valid - cbase;  // valid columns among this thread's
-          if (is_tree && mrow != nullptr) {
-            // All loads first, so that they are in flight together; 16-byte loads where the row
-            // allows it (a thread reads a row of its own, so every load costs a pass per lane).
-            float mv[NC];
-            const float* mp = mrow + col0 + cbase;
-            const bool v4 = (reinterpret_cast<uintptr_t>(mp) & 15) == 0;
-#pragma unroll
-            for (int c = 0; c < NC; c += 4) {
-              if (v4 && c + 3 < vh) {
-                const float4 x = __ldg(reinterpret_cast<const float4*>(mp + c));
-                mv[c] = x.x; mv[c + 1] = x.y; mv[c + 2] = x.z; mv[c + 3] = x.w;
-              } else {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) mv[c + k] = c + k < vh ? __ldg(mp + c + k) : 0.f;
-              }
-            }
-#pragma unroll
-            for (int c = 0; c < NC; ++c) {
-              float v = s[c] * scale2;
-              if (c < vh) v = fmaf(mv[c], FTA_LOG2E, v);
-              else v = -INFINITY;
-              s[c] = v;
-              mx[c & 3] = fmaxf(mx[c & 3], v);
-            }
-          } else {
-#pragma unroll
-            for (int c = 0; c < NC; ++c) {
-              const float v = c < vh ? s[c] * scale2 : -INFINITY;
-              s[c] = v;
-              mx[c & 3] = fmaxf(mx[c & 3], v);
-            }
-          }
-          mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-          mul = 1.f;
-        }
-        // lazy rescale: keep the running max until it is exceeded by more than 2^8; O may only be
-        // touched once the previous PV has finished
-        const bool need = mt > m_used + 8.f;
-        if (i > 0 && __any_sync(0xffffffffu, need)) {
-          ok = wait_all(BAR(B_ODONE + ((t - 1) & 3)), ((t - 1) >> 2) & 1, abort_flag, 0x302);
-          if (!ok) break;
-          tc_fence_after();
-          const float alpha = need ? fta_exp2(m_used - mt) : 1.f;
-#pragma unroll
-          for (int ch = 0; ch < kD / 32; ++ch) {
-            float o[32];
-            tmem_ld32(t_lane + ch * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int k = 0; k < 32; ++k) o[k] *= alpha;
-            tmem_st32(t_lane + ch * 32, o);
-          }
-          tmem_st_wait();
-        }
-        if (need) {
-          l *= fta_exp2(m_used - mt);
-          m_used = mt;
-        }
-        const float nsub = m_used == -INFINITY ? 0.f : -m_used;
-        float ps[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[NC / 2];
-#pragma unroll
-        for (int c2 = 0; c2 < NC / 2; ++c2) {
-          const float2 e = ffma2(make_float2(s[2 * c2], s[2 * c2 + 1]), make_float2(mul, mul), make_float2(nsub, nsub));
-          // every other pair is exponentiated on the FMA pipe, so that the MUFU (4 lanes per
-          // clock) and the FMA pipe work side by side
-          float p0, p1;
-          if (c2 & 1) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
-          else { p0 = fta_exp2(e.x); p1 = fta_exp2(e.y); }
-          ps[c2 & 3] += p0 + p1;
-          pk[c2] = FtaType<T>::pack(p0, p1);
-        }
-        l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-        // P[t%3] was the A operand of PV(t-3), which completed before S(t) was even issued
-        if (row == 0) FTA_TRACE(t, 4);
-        if (CS == 2) tmem_st16(t_lane + kColP + 32 * sbuf + 16 * chalf, pk);
-        else tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
-        if (!is_tree && valid < FTA_TILE) {
-          ok = zero_v_tail(t, valid);
-          if (!ok) break;
-        }
-        tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(BAR(B_PREADY + sbuf));
-        if (row == 0) FTA_TRACE(t, 5);
-      }
-      if (!ok) break;
-
-      // ---- epilogue of the piece: O row / l, LSE ------------------------------------------
-      if (row == 0) FTA_TRACE_EP(sidx - 1, 0);
-      ok = wait_all(BAR(B_ODONE + (t_last & 3)), (t_last >> 2) & 1, abort_flag, 0x304);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t ep_idx = sidx - 1;
-      if (row == 0) FTA_TRACE_EP(ep_idx, 1);
-      // Every MMA of the piece is complete, so the Q columns of TMEM may be rewritten: the next
-      // piece's Q goes in first and its S tiles are computed while this piece's O is stored.
-      if (nhave) {
-        ok = q_to_tmem();
-        if (!ok) break;
-      }
-      if (row == 0) FTA_TRACE_EP(ep_idx, 2);
-      float w0 = 1.f, w1 = 0.f;
-      float* xo = reinterpret_cast<float*>(sm + OFF_X);
-      if (CS == 2) {
-        // The two halves of the tile's rows hold two partial attentions of the same queries (over
-        // the lower / upper 32 columns of every tile).  The upper half parks its unnormalised O row,
-        // maximum and row sum in shared memory (16-byte chunks XOR-swizzled by row: conflict-free);
-        // the lower half folds them into its own while it stores the result.
-        float* xm = xo + 64 * 128;
-        if (chalf == 1) {
-          ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x30a);
+        mbar_arrive(BAR(B_OFREE));
+        if (row == 0) FTA_TRACE_EP(sidx, 4);
+        // The Q buffer is this piece's staging area, but only after the next piece's Q, which has
+        // been sitting in it, went to TMEM.
+        if (nseg.valid) {
+          ok = wait_all(BAR(B_QREADY), (sidx + 1) & 1, abort_flag, 0x503);
           if (!ok) break;
-#pragma unroll
-          for (int ch = 0; ch < kD / 32; ++ch) {
-            float o[32];
-            tmem_ld32(t_lane + ch * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<float4*>(xo + lrow * 128 + (((ch * 8 + j) ^ (lrow & 31)) << 2)) =
-                  make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-          }
-          xm[2 * lrow] = m_used;
-          xm[2 * lrow + 1] = l;
-          tc_fence_before();
-          mbar_arrive(BAR(B_OFREE));
-          mbar_arrive(BAR(B_XFULL));
-        } else {
-          ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x30b);
-          if (!ok) break;
-          const float m1 = xm[2 * lrow], l1 = xm[2 * lrow + 1];
-          const float mstar = fmaxf(m_used, m1);
-          w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
-          w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
-          l = l * w0 + l1 * w1;
-          m_used = mstar;
         }
-        ++xcount;
-      }
-      if (row == 0) FTA_TRACE_EP(ep_idx, 3);
-
-      if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 1 && row == 0)
-        fta_cut_desc(p, g)[blockIdx.x] = make_int4(seg.b, seg.j, seg.nsplit, seg.p0slot);  // for stage 2
-      if (CS == 1 || chalf == 0) {  // uniform per warp: the upper half's warps have nothing to store
-        const bool rstore = rvalid;
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
-        const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
-        const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
-        void* dst;
-        int dt = FTA_DTYPE_F32;
-        long long off = 0;
-        if (final_direct) {
-          dst = p.out; dt = p.out_dtype;
-          if (rstore) {
-            off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
-            if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
-          }
-        } else if (p.split_mode == FTA_SPLIT_BALANCED) {
-          dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
-          if (rstore) ws_l[(long long)seg.slot * g.R + lrow] = lse;
-        } else if (tree_piece) {
-          dst = p.tree_o;
-          if (rstore) {
-            const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
-            off = ro * kD;
-            p.tree_lse[ro] = lse;
-          }
-        } else {
-          dst = p.mid_o;
-          if (rstore) {
-            off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
-            p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
-          }
-        }
-        // O leaves TMEM 32 columns at a time (a thread never holds its whole row) and goes through
-        // the Q buffer, this warp's own 32 rows of it, so that every store instruction of the warp
-        // writes two whole 256-byte row pieces: thread = row on the way in (16-byte chunks
-        // XOR-swizzled by row), 16 lanes per row on the way out.  fp32 rows take two passes of 64
-        // columns, 16-bit rows one pass of 128.
-        const bool wide = dt == FTA_DTYPE_F32 ||
-                          (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((p.o_sb | p.o_sh | p.o_sq) & 7) == 0);
-        uint8_t* stg = sm + OFF_Q;
-        const float f0 = w0 * inv, f1 = w1 * inv;
+        float* xo = reinterpret_cast<float*>(sm + OFF_X);
+        if (CS == 2) {
+          // The two halves of the tile's rows hold two partial attentions of the same queries (over
+          // the lower / upper 32 columns of every tile).  The upper half parks its unnormalised O row,
+          // maximum and row sum in shared memory (16-byte chunks XOR-swizzled by row: conflict-free);
+          // the lower half folds them into its own.
+          float* xm = xo + 64 * 128;
+          if (chalf == 1) {
+            ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x30a);
+            if (!ok) break;
 #pragma unroll
-        for (int ch = 0; ch < kD / 32; ++ch) {
-          float o[32];
-          tmem_ld32(t_lane + ch * 32, o);
-          tmem_ld_wait();
-          if (ch == kD / 32 - 1) {
-            tc_fence_before();
-            mbar_arrive(BAR(B_OFREE));
-          }
-          if (CS == 2) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 v = *reinterpret_cast<const float4*>(xo + lrow * 128 + (((ch * 8 + j) ^ (lrow & 31)) << 2));
-              o[4 * j] = o[4 * j] * f0 + v.x * f1; o[4 * j + 1] = o[4 * j + 1] * f0 + v.y * f1;
-              o[4 * j + 2] = o[4 * j + 2] * f0 + v.z * f1; o[4 * j + 3] = o[4 * j + 3] * f0 + v.w * f1;
-            }
-            if (ch == kD / 32 - 1) mbar_arrive(BAR(B_XFREE));
+            for (int j = 0; j < kD / 4; ++j)
+              *reinterpret_cast<float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2)) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            xm[2 * lrow] = m_used;
+            xm[2 * lrow + 1] = l;
+            mbar_arrive(BAR(B_XFULL));
           } else {
+            ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x30b);
+            if (!ok) break;
+            const float m1 = xm[2 * lrow], l1 = xm[2 * lrow + 1];
+            const float mstar = fmaxf(m_used, m1);
+            const float w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
+            const float w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
 #pragma unroll
-            for (int k = 0; k < 32; ++k) o[k] *= inv;
+            for (int j = 0; j < kD / 4; ++j) {
+              const float4 v = *reinterpret_cast<const float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2));
+              o[4 * j] = o[4 * j] * w0 + v.x * w1; o[4 * j + 1] = o[4 * j + 1] * w0 + v.y * w1;
+              o[4 * j + 2] = o[4 * j + 2] * w0 + v.z * w1; o[4 * j + 3] = o[4 * j + 3] * w0 + v.w * w1;
+            }
+            l = l * w0 + l1 * w1;
+            m_used = mstar;
+            mbar_arrive(BAR(B_XFREE));
           }
+          ++xcount;
+        }
+
+        if (row == 0) FTA_TRACE_EP(8 + sidx, 0);
+        if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 1 && row == 0)
+          fta_cut_desc(p, g)[blockIdx.x] = make_int4(seg.b, seg.j, seg.nsplit, seg.p0slot);  // for stage 2
+        if (CS == 1 || chalf == 0) {  // uniform per warp: the upper half's warps have nothing to store
+          const bool rstore = rvalid;
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
+          const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
+          const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
+          void* dst;
+          int dt = FTA_DTYPE_F32;
+          long long off = 0;
+          if (final_direct) {
+            dst = p.out; dt = p.out_dtype;
+            if (rstore) {
+              off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
+              if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
+            }
+          } else if (p.split_mode == FTA_SPLIT_BALANCED) {
+            dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
+            if (rstore) ws_l[(long long)seg.slot * g.R + lrow] = lse;
+          } else if (tree_piece) {
+            dst = p.tree_o;
+            if (rstore) {
+              const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
+              off = ro * kD;
+              p.tree_lse[ro] = lse;
+            }
+          } else {
+            dst = p.mid_o;
+            if (rstore) {
+              off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
+              p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+            }
+          }
+          // The rows go through the Q buffer, this warp's own 32 rows of it, so that every store
+          // instruction of the warp writes two whole 256-byte row pieces: thread = row on the way in
+          // (16-byte chunks XOR-swizzled by row), 16 lanes per row on the way out.  fp32 rows take two
+          // passes of 64 columns, 16-bit rows one pass of 128.
+          if (row == 0) FTA_TRACE_EP(8 + sidx, 1);
+          const bool wide = dt == FTA_DTYPE_F32 ||
+                            (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((p.o_sb | p.o_sh | p.o_sq) & 7) == 0);
+          uint8_t* stg = sm + OFF_Q;
           if (!wide) {
             if (rstore) {
 #pragma unroll
-              for (int c4 = 0; c4 < 32; c4 += 4)
-                fta_store4(dst, dt, off + ch * 32 + c4, make_float4(o[c4], o[c4 + 1], o[c4 + 2], o[c4 + 3]));
-            }
-            continue;
-          }
-          if (dt == FTA_DTYPE_F32) {
-            if ((ch & 1) == 0) __syncwarp();  // the previous pass has been read out
-            if (rstore) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<uint4*>(stg + (ch & 1) * kQHalf + row * 128 + ((j ^ (row & 7)) << 4)) =
-                    make_uint4(__float_as_uint(o[4 * j]), __float_as_uint(o[4 * j + 1]), __float_as_uint(o[4 * j + 2]),
-                               __float_as_uint(o[4 * j + 3]));
+              for (int c4 = 0; c4 < kD; c4 += 4)
+                fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
             }
           } else {
-            if (rstore) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                if (dt == FTA_DTYPE_F16) {
-                  v.x = FtaType<__half>::pack(o[8 * j], o[8 * j + 1]); v.y = FtaType<__half>::pack(o[8 * j + 2], o[8 * j + 3]);
-                  v.z = FtaType<__half>::pack(o[8 * j + 4], o[8 * j + 5]); v.w = FtaType<__half>::pack(o[8 * j + 6], o[8 * j + 7]);
-                } else {
-                  v.x = FtaType<__nv_bfloat16>::pack(o[8 * j], o[8 * j + 1]); v.y = FtaType<__nv_bfloat16>::pack(o[8 * j + 2], o[8 * j + 3]);
-                  v.z = FtaType<__nv_bfloat16>::pack(o[8 * j + 4], o[8 * j + 5]); v.w = FtaType<__nv_bfloat16>::pack(o[8 * j + 6], o[8 * j + 7]);
-                }
-                const int c = (ch & 1) * 4 + j;
-                *reinterpret_cast<uint4*>(stg + (ch >> 1) * kQHalf + row * 128 + ((c ^ (row & 7)) << 4)) = v;
-              }
-            }
-          }
-          const bool flush = dt == FTA_DTYPE_F32 ? (ch & 1) == 1 : ch == kD / 32 - 1;
-          if (flush) {
-            const int pass = dt == FTA_DTYPE_F32 ? ch >> 1 : 0;
             const uint32_t esize = dt == FTA_DTYPE_F32 ? 4u : 2u;
-            __syncwarp();
-            // all shared-memory reads first, then all stores: neither waits for the other
             const int c = lane & 15;
-            uint4 vals[16];
 #pragma unroll
-            for (int it = 0; it < 16; ++it) {
-              const int rr = quad * 32 + 2 * it + (lane >> 4);
-              vals[it] = *reinterpret_cast<const uint4*>(stg + (c >> 3) * kQHalf + rr * 128 + (((c & 7) ^ (rr & 7)) << 4));
-            }
-            uint8_t* gdst = reinterpret_cast<uint8_t*>(dst) + pass * 256 + c * 16;
+            for (int pass = 0; pass < 2; ++pass) {
+              if (pass == 1 && dt != FTA_DTYPE_F32) break;
+              __syncwarp();  // the previous pass (or piece) has been read out
+              if (rstore) {
 #pragma unroll
-            for (int it = 0; it < 16; ++it) {
-              const int rl = 2 * it + (lane >> 4);
-              const long long roff = __shfl_sync(0xffffffffu, off, rl);
-              const bool rv = __shfl_sync(0xffffffffu, rstore ? 1 : 0, rl) != 0;
-              if (rv) __stcg(reinterpret_cast<uint4*>(gdst + roff * esize), vals[it]);
+                for (int cc = 0; cc < 16; ++cc) {
+                  uint4 v;
+                  if (dt == FTA_DTYPE_F32) {
+                    const int e = pass * 64 + 4 * cc;
+                    v.x = __float_as_uint(o[e] * inv); v.y = __float_as_uint(o[e + 1] * inv);
+                    v.z = __float_as_uint(o[e + 2] * inv); v.w = __float_as_uint(o[e + 3] * inv);
+                  } else if (dt == FTA_DTYPE_F16) {
+                    const int e = 8 * cc;
+                    v.x = FtaType<__half>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__half>::pack(o[e + 2] * inv, o[e + 3] * inv);
+                    v.z = FtaType<__half>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__half>::pack(o[e + 6] * inv, o[e + 7] * inv);
+                  } else {
+                    const int e = 8 * cc;
+                    v.x = FtaType<__nv_bfloat16>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__nv_bfloat16>::pack(o[e + 2] * inv, o[e + 3] * inv);
+                    v.z = FtaType<__nv_bfloat16>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__nv_bfloat16>::pack(o[e + 6] * inv, o[e + 7] * inv);
+                  }
+                  *reinterpret_cast<uint4*>(stg + (cc >> 3) * kQHalf + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = v;
+                }
+              }
+              if (row == 0) FTA_TRACE_EP(8 + sidx, 2 + 3 * pass);
+              __syncwarp();
+              uint8_t* gdst = reinterpret_cast<uint8_t*>(dst) + pass * 256 + c * 16;
+#pragma unroll 4
+              for (int it = 0; it < 16; ++it) {
+                const int rl = 2 * it + (lane >> 4);
+                const int rr = quad * 32 + rl;
+                const uint4 v = *reinterpret_cast<const uint4*>(stg + (c >> 3) * kQHalf + rr * 128 + (((c & 7) ^ (rr & 7)) << 4));
+                const long long roff = __shfl_sync(0xffffffffu, off, rl);
+                const bool rv = __shfl_sync(0xffffffffu, rstore ? 1 : 0, rl) != 0;
+                if (rv) __stcg(reinterpret_cast<uint4*>(gdst + roff * esize), v);
+              }
+              if (row == 0) FTA_TRACE_EP(8 + sidx, 3 + 3 * pass);
             }
+            __syncwarp();
+            if (row == 0) FTA_TRACE_EP(8 + sidx, 4);
           }
         }
-        __syncwarp();
       }
-      if (row == 0) FTA_TRACE_EP(ep_idx, 6);
-      if (nhave) {  // the staging area is the next Q tile's again
+      if (row == 0) FTA_TRACE_EP(sidx, 6);
+      if (nseg.valid) {  // the staging area is the Q buffer of the piece after next again
         fence_proxy_async();
         mbar_arrive(BAR(B_QEMPTY));
       }
+      if (lane == 0) mbar_arrive(BAR(B_SEGFREE + sidx % kSegRing));
       gt += n;
+      ++sidx;
       seg = nseg;
-      have = nhave;
     }
   }
 
@@ -835,9 +914,9 @@ EncodeTiledFn get_encode() {
 struct MapKey {
   const void* ptr;
   int dtype;
-  uint64_t dims[4];
-  int64_t strides[3];
-  uint32_t box[4];
+  uint64_t dims[5];
+  int64_t strides[4];
+  uint32_t box[5];
   bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
 struct MapEntry {
@@ -850,33 +929,48 @@ MapEntry g_maps[kMapCache];
 int g_map_next = 0;
 std::mutex g_map_mu;
 
-// 4-D map over a [B, heads, rows, 128] tensor with element strides (rows, heads, batch);
-// box = 64 columns x box_rows x box_heads x 1, 128-byte swizzle, zero fill out of bounds.
+// Map over a [B, heads, rows, 128] tensor with element strides (rows, heads, batch); boxes of 64
+// columns (one 128-byte swizzle span) x box_rows x box_heads, zero fill out of bounds.
+//   both_halves: 5-D, the two halves of the 128 columns are a dimension of their own placed after
+//                the heads, so that ONE copy lands as [half][row][64 columns] (K and V tiles: the
+//                second half starts box_rows * 128 bytes after the first);
+//   otherwise:   4-D, one copy per half (the Q tile, whose halves sit 128 rows apart whatever the
+//                number of rows the box has).
 bool make_map(CUtensorMap* out, const void* ptr, int dtype, uint64_t rows, uint64_t heads, uint64_t B, int64_t s_row,
-              int64_t s_head, int64_t s_batch, uint32_t box_rows, uint32_t box_heads) {
+              int64_t s_head, int64_t s_batch, uint32_t box_rows, uint32_t box_heads, bool both_halves) {
   MapKey key;
   memset(&key, 0, sizeof(key));
   key.ptr = ptr; key.dtype = dtype;
-  key.dims[0] = kD; key.dims[1] = rows; key.dims[2] = heads; key.dims[3] = B;
+  key.dims[0] = both_halves ? 64 : kD; key.dims[1] = rows; key.dims[2] = heads; key.dims[3] = both_halves ? 2 : 1; key.dims[4] = B;
   // a stride of a size-1 dimension is never used; give it a value the encoder accepts
   if (heads == 1) s_head = s_row * (int64_t)rows;
   if (B == 1) s_batch = s_head * (int64_t)heads;
   if (rows == 1) s_row = kD;
-  key.strides[0] = s_row; key.strides[1] = s_head; key.strides[2] = s_batch;
-  key.box[0] = 64; key.box[1] = box_rows; key.box[2] = box_heads; key.box[3] = 1;
+  key.strides[0] = s_row; key.strides[1] = s_head; key.strides[2] = 64; key.strides[3] = s_batch;
+  key.box[0] = 64; key.box[1] = box_rows; key.box[2] = box_heads; key.box[3] = both_halves ? 2 : 1; key.box[4] = 1;
   std::lock_guard<std::mutex> lock(g_map_mu);
   for (int i = 0; i < kMapCache; ++i)
     if (g_maps[i].used && g_maps[i].key == key) { *out = g_maps[i].map; return true; }
   EncodeTiledFn enc = get_encode();
   if (!enc) return false;
-  cuuint64_t gdim[4] = {key.dims[0], key.dims[1], key.dims[2], key.dims[3]};
-  cuuint64_t gstr[3] = {(cuuint64_t)s_row * 2, (cuuint64_t)s_head * 2, (cuuint64_t)s_batch * 2};
-  cuuint32_t box[4] = {key.box[0], key.box[1], key.box[2], key.box[3]};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
+  cuuint64_t gdim[5] = {key.dims[0], key.dims[1], key.dims[2], key.dims[3], key.dims[4]};
+  cuuint64_t gstr[4] = {(cuuint64_t)s_row * 2, (cuuint64_t)s_head * 2, 128, (cuuint64_t)s_batch * 2};
+  cuuint32_t box[5] = {key.box[0], key.box[1], key.box[2], key.box[3], key.box[4]};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUtensorMap m;
-  CUresult r = enc(&m, dtype == FTA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                   const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUtensorMapDataType dt = dtype == FTA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r;
+  if (both_halves) {
+    r = enc(&m, dt, 5, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    // 4-D: {128 columns, rows, heads, batch}, box of 64 columns; the caller loads the halves one by one
+    cuuint64_t gdim4[4] = {(cuuint64_t)kD, key.dims[1], key.dims[2], key.dims[4]};
+    cuuint64_t gstr4[3] = {(cuuint64_t)s_row * 2, (cuuint64_t)s_head * 2, (cuuint64_t)s_batch * 2};
+    cuuint32_t box4[4] = {64, box_rows, box_heads, 1};
+    r = enc(&m, dt, 4, const_cast<void*>(ptr), gdim4, gstr4, box4, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) return false;
   MapEntry& e = g_maps[g_map_next];
   g_map_next = (g_map_next + 1) % kMapCache;
@@ -936,12 +1030,12 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
 
   Maps maps;
   const int Hcur = p.Hkv * p.cur_head_mul;
-  bool ok = make_map(&maps.q, p.q, p.dtype, p.Q, p.H, p.B, p.q_sq, p.q_sh, p.q_sb, g.qpt, g.hpt) &&
-            make_map(&maps.k, p.k_cache, p.dtype, p.ctx, p.Hkv, p.B, p.k_st, p.k_sh, p.k_sb, FTA_TILE, 1) &&
-            make_map(&maps.v, p.v_cache, p.dtype, p.ctx, p.Hkv, p.B, p.v_st, p.v_sh, p.v_sb, FTA_TILE, 1);
+  bool ok = make_map(&maps.q, p.q, p.dtype, p.Q, p.H, p.B, p.q_sq, p.q_sh, p.q_sb, g.qpt, g.hpt, false) &&
+            make_map(&maps.k, p.k_cache, p.dtype, p.ctx, p.Hkv, p.B, p.k_st, p.k_sh, p.k_sb, FTA_TILE, 1, true) &&
+            make_map(&maps.v, p.v_cache, p.dtype, p.ctx, p.Hkv, p.B, p.v_st, p.v_sh, p.v_sb, FTA_TILE, 1, true);
   if (ok && p.with_tree) {
-    ok = make_map(&maps.ck, p.cur_k, p.dtype, p.Q, Hcur, p.B, p.ck_st, p.ck_sh, p.ck_sb, FTA_TILE, 1) &&
-         make_map(&maps.cv, p.cur_v, p.dtype, p.Q, Hcur, p.B, p.cv_st, p.cv_sh, p.cv_sb, FTA_TILE, 1);
+    ok = make_map(&maps.ck, p.cur_k, p.dtype, p.Q, Hcur, p.B, p.ck_st, p.ck_sh, p.ck_sb, FTA_TILE, 1, true) &&
+         make_map(&maps.cv, p.cur_v, p.dtype, p.Q, Hcur, p.B, p.cv_st, p.cv_sh, p.cv_sb, FTA_TILE, 1, true);
   } else if (ok) {
     maps.ck = maps.k;
     maps.cv = maps.v;
