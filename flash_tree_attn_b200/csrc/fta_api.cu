@@ -141,9 +141,12 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
   g.U = p.Hkv * g.mtiles;
   g.n_tree = p.with_tree ? fta_cdiv(p.Q, FTA_TILE) : 0;
   g.min_per = 2;
+  g.pad = 0;
   g.fixed_max_splits = (p.split_mode == FTA_SPLIT_FIXED && p.split_tokens > 0) ? fta_cdiv(p.ctx, p.split_tokens) : 0;
   g.family = fam;
   g.cs = (fam == FTA_KERNEL_UMMA && g.hpt * g.qpt <= 64) ? 2 : 1;
+  // measured cost of ending a unit, in tile times of the family's steady state
+  if (fam == FTA_KERNEL_UMMA) g.pad = g.cs == 2 ? 8 : 4;
   g.grid = p.grid_override > 0 ? p.grid_override : 1;
   if (!need_grid || p.grid_override > 0) return FTA_OK;
 
@@ -297,10 +300,10 @@ int64_t fta_plan_host(const FtaParams* p, const int64_t* lens, int64_t* segs_out
   std::vector<int> pre(q.B + 1, 0);
   for (int b = 0; b < q.B; ++b) {
     const int L = fta_load_len(lens, 1, b, q.ctx);
-    pre[b + 1] = pre[b] + fta_cdiv(L, FTA_TILE) + g.n_tree;
+    pre[b + 1] = pre[b] + fta_unit_tiles(L, g.n_tree, g.pad);
   }
   FtaBalanced plan;
-  plan.pre = pre.data(); plan.B = q.B; plan.U = g.U; plan.n_tree = g.n_tree;
+  plan.pre = pre.data(); plan.B = q.B; plan.U = g.U; plan.n_tree = g.n_tree; plan.pad = g.pad;
   plan.total = (long long)g.U * pre[q.B];
   plan.per = FtaBalanced::choose_per(plan.total, g.grid, g.min_per);
   if (grid_out) *grid_out = g.grid;
@@ -312,6 +315,7 @@ int64_t fta_plan_host(const FtaParams* p, const int64_t* lens, int64_t* segs_out
     while (lin < end) {
       FtaSeg s;
       lin = plan.segment_at(c, lin, s);
+      if (fta_seg_empty(s)) continue;
       const int L = fta_load_len(lens, 1, s.b, q.ctx);
       if (s.c1 > L) s.c1 = L;
       if (segs_out && n < max_segs) {

@@ -32,6 +32,7 @@ struct FtaGeom {
   int fixed_max_splits; // FIXED: ceil(ctx / split_tokens)
   int family;  // FTA_KERNEL_MMA or FTA_KERNEL_UMMA
   int cs;      // tcgen05 family: column split (2 when a unit has at most 64 query rows, else 1)
+  int pad;     // BALANCED: what ending a unit costs a block, in tiles (see FtaBalanced)
 };
 
 // One contiguous piece of one unit, processed by one block without interruption.
@@ -58,12 +59,21 @@ __host__ __device__ __forceinline__ int fta_load_len(const void* lens, int is_i6
 
 // ---- BALANCED plan ---------------------------------------------------------------------
 // All units' tiles are laid on one line, sequence-major then unit then tile; a unit of
-// sequence b has ut_b = ceil(L_b/64) + n_tree tiles (cache tiles, then tree tiles).
-// pre[b] = sum_{b'<b} ut_b'.  Unit (b, j) starts at U*pre[b] + j*ut_b.  Block c owns
-// the tiles [c*per, (c+1)*per).  A unit cut by k block boundaries has k+1 pieces.
+// sequence b has ceil(L_b/64) cache tiles, then n_tree tree tiles, then `pad` virtual tiles that
+// stand for the work of ending a unit (last partial tile, tree tile, epilogue, pipeline restart):
+// ut_b = real_b + pad, or 0 for a unit without real tiles.  pre[b] = sum_{b'<b} ut_b'.  Unit (b, j)
+// starts at U*pre[b] + j*ut_b.  Block c owns the line positions [c*per, (c+1)*per), so blocks that
+// end more units get fewer real tiles.  A unit whose real tiles are cut by k block boundaries has
+// k+1 pieces; a range that covers only virtual tiles of a unit gives an empty piece, which callers skip.
+__host__ __device__ __forceinline__ int fta_unit_tiles(int L, int n_tree, int pad) {
+  const int real = (L + FTA_TILE - 1) / FTA_TILE + n_tree;
+  return real > 0 ? real + pad : 0;
+}
+__host__ __device__ __forceinline__ bool fta_seg_empty(const FtaSeg& s) { return s.c1 <= s.c0 && s.tt1 <= s.tt0; }
+
 struct FtaBalanced {
   const int* pre;  // [B+1]
-  int B, U, n_tree, per;
+  int B, U, n_tree, per, pad;
   long long total;
 
   __host__ __device__ static int choose_per(long long total, int grid, int min_per) {
@@ -98,15 +108,19 @@ struct FtaBalanced {
     const int t0 = (int)(boff - (I)j * (I)ut);
     const I ustart = lin - (I)t0, uend = ustart + (I)ut;
     const I send = cend < uend ? cend : uend;
-    const int t1 = t0 + (int)(send - lin);
-    const int nb = ut - n_tree;  // cache tiles of this unit
-    const int cfirst = (int)(ustart / (I)per), clast = (int)((uend - 1) / (I)per);
+    const int nreal = ut - pad;      // cache + tree tiles of this unit
+    const int nb = nreal - n_tree;   // cache tiles
+    int t1 = t0 + (int)(send - lin);
+    const int r0 = t0 < nreal ? t0 : nreal;  // the real part of [t0, t1)
+    t1 = t1 < nreal ? t1 : nreal;
+    const int cfirst = (int)(ustart / (I)per), clast = (int)((ustart + (I)(nreal - 1)) / (I)per);
     s.b = b;
     s.j = j;
-    s.c0 = (t0 < nb ? t0 : nb) * FTA_TILE;
+    s.c0 = (r0 < nb ? r0 : nb) * FTA_TILE;
     s.c1 = (t1 < nb ? t1 : nb) * FTA_TILE;  // caller clamps to L_b
-    s.tt0 = (t0 > nb ? t0 : nb) - nb;
+    s.tt0 = (r0 > nb ? r0 : nb) - nb;
     s.tt1 = (t1 > nb ? t1 : nb) - nb;
+    if (s.tt1 < s.tt0) s.tt1 = s.tt0;
     s.split = c - cfirst;
     s.nsplit = clast - cfirst + 1;
     s.slot = 2 * c + (lin == cbeg ? 0 : 1);
@@ -124,7 +138,7 @@ struct FtaBalanced {
     const int ut = pre[b + 1] - pre[b];
     if (ut == 0) { cfirst = 0; ustart = 0; return 0; }
     ustart = (long long)U * pre[b] + (long long)j * ut;
-    const long long uend = ustart + ut;
+    const long long uend = ustart + ut - pad;  // end of the real tiles
     cfirst = (int)(ustart / per);
     return (int)((uend - 1) / per) - cfirst + 1;
   }
@@ -190,7 +204,7 @@ __device__ __forceinline__ int4* fta_cut_desc(const FtaParams& p, const FtaGeom&
 
 // Block-cooperative build of the prefix table pre[0..B] in shared memory (warp 0 scans).
 // Must be followed by __syncthreads().
-__device__ __forceinline__ void fta_build_prefix(const FtaParams& p, int n_tree, int* pre) {
+__device__ __forceinline__ void fta_build_prefix(const FtaParams& p, int n_tree, int pad, int* pre) {
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
     int carry = 0;
@@ -198,7 +212,7 @@ __device__ __forceinline__ void fta_build_prefix(const FtaParams& p, int n_tree,
     for (int base = 0; base < p.B; base += 32) {
       const int b = base + lane;
       int v = 0;
-      if (b < p.B) v = fta_cdiv(fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx), FTA_TILE) + n_tree;
+      if (b < p.B) v = fta_unit_tiles(fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx), n_tree, pad);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, v, o);

@@ -117,9 +117,9 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
   FtaBalanced plan;
   long long lin = 0, lin_end = 0, item = 0, n_items = 0;
   if (p.split_mode == FTA_SPLIT_BALANCED) {
-    fta_build_prefix(p, g.n_tree, pre);
+    fta_build_prefix(p, g.n_tree, g.pad, pre);
     __syncthreads();
-    plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree;
+    plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree; plan.pad = g.pad;
     plan.total = (long long)g.U * pre[p.B];
     plan.per = FtaBalanced::choose_per(plan.total, gridDim.x, g.min_per);
     lin = (long long)blockIdx.x * plan.per;
@@ -137,6 +137,7 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
     if (p.split_mode == FTA_SPLIT_BALANCED) {
       if (lin >= lin_end) break;
       lin = plan.segment_at(blockIdx.x, lin, seg);
+      if (fta_seg_empty(seg)) continue;  // only the virtual tail of a unit
       Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, seg.b, p.ctx);
       if (seg.c1 > Lb) seg.c1 = Lb;
     } else {

@@ -92,7 +92,7 @@ struct Walker {
   __device__ Walker(const FtaParams& p_, const FtaGeom& g_, const int* pre) : p(p_), g(g_) {
     lin = lin_end = item = n_items = 0;
     if (p.split_mode == FTA_SPLIT_BALANCED) {
-      plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree;
+      plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree; plan.pad = g.pad;
       plan.total = (long long)g.U * pre[p.B];
       plan.per = FtaBalanced::choose_per(plan.total, gridDim.x, g.min_per);
       lin = (long long)blockIdx.x * plan.per;
@@ -104,8 +104,10 @@ struct Walker {
   }
   __device__ bool next(FtaSeg& seg) {
     if (p.split_mode == FTA_SPLIT_BALANCED) {
-      if (lin >= lin_end) return false;
-      lin = plan.segment_at(blockIdx.x, lin, seg);
+      do {  // ranges that cover only the virtual tail of a unit hold no work
+        if (lin >= lin_end) return false;
+        lin = plan.segment_at(blockIdx.x, lin, seg);
+      } while (fta_seg_empty(seg));
       const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, seg.b, p.ctx);
       if (seg.c1 > Lb) seg.c1 = Lb;
       return true;
@@ -211,7 +213,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if ((r & (kR / CS - 1)) >= box_rows) reinterpret_cast<uint4*>(sm + OFF_Q)[i] = make_uint4(0, 0, 0, 0);
     }
   }
-  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, pre);
+  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, g.pad, pre);
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -510,6 +512,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
           if (!ok) break;
           if (row == 0) FTA_TRACE(t, 3);
+          if (row == 0 && t == 0) FTA_BLK(0, clock64() - prof_t0);
           tc_fence_after();
           float s[NC];
 #pragma unroll
@@ -642,6 +645,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if (seg.valid) ok = q_to_tmem(sidx);
       if (row == 0) FTA_TRACE_EP(sidx - 1, 2);
     }
+    if (row == 0) { FTA_BLK(1, clock64() - prof_t0); FTA_BLK(3, (long long)sidx); }
   } else {
     // ================================ epilogue =======================================
     // O row / l and the LSE of every piece, while the softmax warps are already at work on the
@@ -870,6 +874,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       ++sidx;
       seg = nseg;
     }
+    if (row == 0) FTA_BLK(2, clock64() - prof_t0);
   }
 
 #ifdef FTA_UMMA_PROFILE
@@ -1048,6 +1053,9 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
 #ifdef FTA_UMMA_PROFILE
 extern "C" int fta_umma_trace(long long* out512) {
   return cudaMemcpyFromSymbol(out512, g_umma_trace, sizeof(long long) * 640) == cudaSuccess ? 0 : -1;
+}
+extern "C" int fta_umma_blocks(long long* out4096) {
+  return cudaMemcpyFromSymbol(out4096, g_umma_blk, sizeof(long long) * 4096) == cudaSuccess ? 0 : -1;
 }
 extern "C" int fta_umma_prof(unsigned long long* out64) {
   unsigned long long zero[160] = {0};

@@ -30,6 +30,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// non-blocking form, for a thread that polls more than one barrier
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
 // Every wait in the kernel is bounded: after kWaitCycles the waiter records where it gave up
 // (a code in a device status word), raises the block-wide abort flag and returns false; all
 // other waiters see the flag and leave too, so a protocol error ends the kernel instead of
@@ -54,6 +65,12 @@ __device__ long long g_umma_trace_t0;
   do {                                                                                   \
     if (blockIdx.x == 0 && (tile) < 64u) g_umma_trace[(tile) * 8 + (ev)] = clock64() - g_umma_trace_t0; \
   } while (0)
+// per block: [0] first S tile seen, [1] softmax warps done, [2] epilogue warps done, [3] pieces
+__device__ long long g_umma_blk[1024 * 4];
+#define FTA_BLK(slot, value)                                                             \
+  do {                                                                                   \
+    if (blockIdx.x < 1024u) g_umma_blk[blockIdx.x * 4 + (slot)] = (value);               \
+  } while (0)
 #define FTA_TRACE_EP(piece, ev)                                                          \
   do {                                                                                   \
     if (blockIdx.x == 0 && (piece) < 16u) g_umma_trace[(64 + (piece)) * 8 + (ev)] = clock64() - g_umma_trace_t0; \
@@ -62,10 +79,11 @@ __device__ long long g_umma_trace_t0;
 #define FTA_PROF_ADD(code, cycles) do {} while (0)
 #define FTA_TRACE(tile, ev) do {} while (0)
 #define FTA_TRACE_EP(piece, ev) do {} while (0)
+#define FTA_BLK(slot, value) do {} while (0)
 #endif
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int code) {
-#ifdef FTA_UMMA_PROFILE
+#if defined(FTA_UMMA_PROFILE) && !defined(FTA_UMMA_TRACE_ONLY)
   const long long t0 = clock64();
   for (;;) {
     if (mbar_try_wait(bar, parity)) { FTA_PROF_ADD(code, clock64() - t0); return true; }
