@@ -141,12 +141,11 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
   g.U = p.Hkv * g.mtiles;
   g.n_tree = p.with_tree ? fta_cdiv(p.Q, FTA_TILE) : 0;
   g.min_per = 2;
-  g.pad = 0;
   g.fixed_max_splits = (p.split_mode == FTA_SPLIT_FIXED && p.split_tokens > 0) ? fta_cdiv(p.ctx, p.split_tokens) : 0;
   g.family = fam;
   g.cs = (fam == FTA_KERNEL_UMMA && g.hpt * g.qpt <= 64) ? 2 : 1;
   // measured cost of ending a unit, in tile times of the family's steady state
-  if (fam == FTA_KERNEL_UMMA) g.pad = g.cs == 2 ? 8 : 4;
+  g.pad = (fam == FTA_KERNEL_UMMA && g.cs == 2) ? 8 : 4;
   g.grid = p.grid_override > 0 ? p.grid_override : 1;
   if (!need_grid || p.grid_override > 0) return FTA_OK;
 

@@ -118,8 +118,19 @@ def test_plan_is_balanced_for_ragged_batch(fta_lib):
     rng = random.Random(5)
     lens = [rng.randint(16, 16384) for _ in range(128)]
     rows, g, per = plan(fta_lib, lens, 32, 32, 4, 128, 296)
-    total = sum(-(-L // 64) + 1 for L in lens) * 32
+    # every unit is charged 4 tiles on top of its own (cache tiles + 1 tree tile) for ending: blocks
+    # that finish many short units get fewer tiles to stream
+    pad = 4
+    total = sum(-(-L // 64) + 1 + pad for L in lens) * 32
     assert per == -(-total // 296)
+    cost = {}
+    ends = {}
+    for (c, b, j, c0, c1, t0, t1, packed) in rows:
+        cost[c] = cost.get(c, 0) + (-(-max(c1 - c0, 0) // 64)) + (t1 - t0)
+        if t1 == 1:  # the piece that ends its unit
+            ends[c] = ends.get(c, 0) + 1
+    # a block's tiles plus the charge of the units that end well inside it never exceed its share
+    assert max(cost[c] + pad * max(ends.get(c, 0) - 1, 0) for c in cost) <= per
     # at most two cut pieces per block, so partial slots 2*block + {0,1} never collide
     cut = {}
     for (c, b, j, c0, c1, t0, t1, packed) in rows:
