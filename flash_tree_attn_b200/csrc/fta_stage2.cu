@@ -146,7 +146,9 @@ __global__ void __launch_bounds__(kThreads) merge_parts_kernel(const FtaMergePar
 
 cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
   const bool balanced = p.split_mode == FTA_SPLIT_BALANCED;
-  const dim3 grid(balanced ? g.grid : p.B * g.U, (g.R + kRowsPerBlock - 1) / kRowsPerBlock);
+  // rows past hpt * qpt of a unit's tile are padding: no blocks for them
+  const int rows = g.hpt * g.qpt < g.R ? g.hpt * g.qpt : g.R;
+  const dim3 grid(balanced ? g.grid : p.B * g.U, (rows + kRowsPerBlock - 1) / kRowsPerBlock);
   stage2_kernel<<<grid, kThreads, 0, st>>>(p, g);
   if (balanced && !p.with_tree) empty_rows_kernel<<<p.B, kThreads, 0, st>>>(p);
   return cudaGetLastError();
