@@ -1,32 +1,41 @@
 // Stage 1, tcgen05 family: split-KV tree attention with both products on the 5th-generation
 // tensor cores.  One thread block owns one M tile of 128 rows (all tree queries x the GQA
-// heads that share a KV head) and streams 64-row KV tiles:
+// heads that share a KV head) and streams 64-row KV tiles.  384 threads, three warpgroups:
 //
-//   warp 0      TMA producer: Q once per piece of work, then K and V tiles (two 64-column
-//               boxes each, 128-byte swizzle) into a 5- or 6-stage ring guarded by mbarriers;
-//               K tiles are requested two tiles ahead of V tiles, as they are consumed
-//   warp 1      issuer of S = Q K^T (128x64, fp32 in TMEM, double-buffered, up to two tiles
-//               ahead of the softmax)
-//   warp 6      issuer of O += P V (128x128, fp32 in TMEM).  The A operands Q and P are read
+//   warp 0      TMA producer: Q once per piece of work (two 4-D copies), then one 5-D copy per K
+//               and per V tile (64 rows x 2 halves of 64 columns, 128-byte swizzle) into a 5- or
+//               6-stage ring guarded by mbarriers; K tiles are requested two tiles ahead of V tiles
+//   warp 1      issuer of S = Q K^T (128x64, fp32 in TMEM, three buffers, up to three tiles ahead
+//               of the softmax)
+//   warp 2      issuer of O += P V (128x128, fp32 in TMEM).  The A operands Q and P are read
 //               from TMEM, so only K and V cross shared memory; completion of either product is
 //               signalled by tcgen05.commit.  Two issuers because one thread cannot feed the
 //               tensor pipe with 12 small products per tile and answer five barriers in time
-//   warps 2..5  softmax: a thread owns one row (TMEM lane): copies its Q row into TMEM at the
+//   warp 3      planner: walks the block's pieces of work once and hands each to the other roles
+//               as a 64-byte descriptor in a shared-memory ring
+//   warps 4..7  softmax: a thread owns one row (TMEM lane): copies its Q row into TMEM at the
 //               start of a piece; per tile tcgen05.ld of S, scale, tree mask / sequence-end
-//               mask, running max with lazy rescale of O, exp2, P (16-bit pairs) stored to
-//               TMEM; at the end of a piece the normalised O row and its LSE
+//               mask, running max with lazy rescale of O, exp2 (half of them on the FMA pipe),
+//               P (16-bit pairs) stored to TMEM; at the end of a piece the row's maximum and sum
+//               go to the epilogue warps through two TMEM columns and the next piece starts
+//   warps 8..11 epilogue: read a finished piece's O rows from TMEM (handing the accumulator back at
+//               once), normalise, stage through the Q buffer and store 256-byte row pieces, and the
+//               LSE; all of it beside the next piece's tiles
+//
+// Registers are rebalanced with setmaxnreg (64 per thread for warps 0..3, 240 for the softmax, 200
+// for the epilogue).
 //
 // Column split (template CS = 2): when a unit has at most 64 query rows (q_len 64 without GQA),
 // rows 64..127 of the tile repeat rows 0..63 (Q is loaded twice) and each half of the tile's rows
 // works on its own 32 of every tile's 64 KV columns, with its own running max, row sum and O rows.
 // Half of each P row is then zero, the two O halves are two partial attentions of the same query
-// and are merged through shared memory at the end of a piece.  The tensor work is unchanged (the
+// and are merged through shared memory by the epilogue warps.  The tensor work is unchanged (the
 // tile has 128 rows either way) but all four schedulers share the exponentials.
 //
 // It replaces the reference's _flash_decoding_fwd_kernel (flash_tree_attn.py:14-144) and the
 // eager tree tail (flash_tree_attn.py:367-371) for head_dim 128 when M = G*Q is large enough
-// to fill a 128-row tile usefully; the work plan, the partial-result slots and the epilogue
-// are those of the warp-MMA family.
+// to fill a 128-row tile usefully; the work plan and the partial-result slots are those of the
+// warp-MMA family.
 //
 // Every mbarrier wait is bounded (fta_umma_ptx.cuh); on a timeout the block records a code in
 // g_umma_status, all roles leave their loops, and the block still frees its TMEM.
@@ -1002,6 +1011,11 @@ int fta_umma_supported(const FtaParams& p) {
     if (p.Hkv * p.cur_head_mul > 1 && (!stride_ok(p.ck_sh) || !stride_ok(p.cv_sh))) return 0;
     if (p.B > 1 && (!stride_ok(p.ck_sb) || !stride_ok(p.cv_sb))) return 0;
   }
+  // the block's shared memory (prefix table of B + 1 entries included) must fit with five stages
+  const int G = p.H / p.Hkv;
+  const int qpt = p.Q < kR ? p.Q : kR;
+  const int hpt = kR / qpt < G ? kR / qpt : G;
+  if (smem_bytes(5, p.B, hpt * qpt <= 64 ? 2 : 1) > 227 * 1024) return 0;
   return get_encode() != nullptr ? 1 : 0;
 }
 

@@ -134,6 +134,24 @@ def test_result_independent_of_split_count(fta, grid, kernel):
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("B,Q,G", [(96, 64, 1), (40, 26, 4), (700, 64, 1)])
+def test_many_short_sequences(fta, B, Q, G, kernel):
+    """Dozens of units per block, most of them one or two tiles long: every block ends many
+    units, the ring of piece descriptors wraps, and (B = 700) the prefix table of the lengths is
+    large."""
+    from flash_tree_attn_b200.workloads import make_inputs
+    import random
+
+    fta.set_kernel(kernel)
+    rng = random.Random(B)
+    lens = [rng.choice([0, 1, 5, 63, 64, 65, 100, 130, 200]) for _ in range(B)]
+    w = _workload(B=B, H=2 * G, G=G, D=128, Q=Q, ctx=256, lens="fixed:" + ",".join(map(str, lens)))
+    inp = make_inputs(w, "cuda")
+    out, lse = _run(fta, inp, G, ctx=256)
+    _check(out, lse, _oracle(inp, G), f"B={B} Q={Q} G={G}")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
 def test_padding_rows_are_never_read(fta, kernel):
     """NaN in every cache row at or past kv_seq_len must not reach the result (the reference
     needs finite padding, flash_tree_attn.py:93-94)."""
