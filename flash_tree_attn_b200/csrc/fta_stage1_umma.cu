@@ -71,9 +71,9 @@ constexpr uint32_t kColQ = 320;  // 64 columns: 128 head-dim elements, two per c
 constexpr uint32_t kColP = 384;  // + 32 * buffer: 64 KV columns, two per column
 constexpr uint32_t kColStat = 480;  // a row's running maximum and sum, handed from the softmax to the epilogue warps
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
-constexpr uint32_t kXBytes = 64 * 128 * 4 + 64 * 2 * 4;  // CS = 2: one unnormalised O half + (m, l) per query row
+constexpr uint32_t kXBytes = 2 * 64 * 64 * 4 + 2 * 64 * 2 * 4;  // CS = 2: per half 64 rows x 64 unnormalised O columns, and (m, l) per row
 constexpr size_t smem_bytes(int ns, int B, int cs) {
-  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + kSegBytes + (size_t)(B + 1) * 4 + 1024;
+  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + kSegBytes + (size_t)(B + 1) * 4 + (cs == 2 ? 0 : 1024);
 }
 
 // mbarrier slots (ring barriers are sized for the largest ring)
@@ -180,9 +180,18 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   constexpr uint32_t OFF_BAR = OFF_X + (CS == 2 ? kXBytes : 0);
   constexpr uint32_t OFF_SEG = OFF_BAR + kBarBytes;
   constexpr uint32_t OFF_PRE = OFF_SEG + kSegBytes;
-  extern __shared__ uint8_t smem_raw[];
+  // Swizzle atoms are 1024-byte aligned.  Without the column split there is room to round the base
+  // up; with it every kilobyte is taken, the declared alignment is relied on and checked.
+  extern __shared__ uint8_t smem_plain[];
+  extern __shared__ __align__(1024) uint8_t smem_aligned[];  // the same memory, alignment declared
+  uint8_t* smem_raw;
+  if constexpr (CS == 2) smem_raw = smem_aligned; else smem_raw = smem_plain;
   const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzle atoms are 1024-byte aligned
+  const uint32_t base = CS == 2 ? raw : ((raw + 1023u) & ~1023u);
+  if (CS == 2 && (base & 1023u)) {  // never seen; without the alignment nothing below may run
+    if (threadIdx.x == 0) atomicCAS(&g_umma_status, 0u, 0x7ffu);
+    return;
+  }
   uint8_t* sm = smem_raw + (base - raw);
   int* pre = reinterpret_cast<int*>(sm + OFF_PRE);
   SegDesc* segq = reinterpret_cast<SegDesc*>(sm + OFF_SEG);
@@ -207,7 +216,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     if (tid == B_QEMPTY || tid == B_QREADY || tid == B_OFREE || tid == B_STATS || tid == B_STATSFREE ||
         (tid >= B_PREADY && tid < B_PREADY + kNBuf))
       count = 128;
-    else if (tid == B_XFULL || tid == B_XFREE) count = 64;
+    else if (tid == B_XFULL || tid == B_XFREE) count = 128;
     else if (tid >= B_SEGFREE && tid < B_SEGFREE + kSegRing) count = 4;
     mbar_init(BAR(tid), count);
     fence_barrier_init();
@@ -715,15 +724,10 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           if (!ok) break;
         }
         if (CS == 2) {  // keep the halves' exchange barriers in step
-          if (chalf == 1) {
-            ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x315);
-            if (!ok) break;
-            mbar_arrive(BAR(B_XFULL));
-          } else {
-            ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x316);
-            if (!ok) break;
-            mbar_arrive(BAR(B_XFREE));
-          }
+          ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x315);
+          if (!ok) break;
+          mbar_arrive(BAR(B_XFULL));
+          mbar_arrive(BAR(B_XFREE));
           ++xcount;
         }
       } else {
@@ -742,134 +746,253 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           ok = wait_all(BAR(B_QREADY), (sidx + 1) & 1, abort_flag, 0x503);
           if (!ok) break;
         }
-        float* xo = reinterpret_cast<float*>(sm + OFF_X);
+        constexpr int NCOL = CS == 2 ? 64 : kD;   // output columns this thread stores
+        const int col0 = CS == 2 ? 64 * chalf : 0;  // the first of them
         if (CS == 2) {
           // The two halves of the tile's rows hold two partial attentions of the same queries (over
-          // the lower / upper 32 columns of every tile).  The upper half parks its unnormalised O row,
-          // maximum and row sum in shared memory (16-byte chunks XOR-swizzled by row: conflict-free);
-          // the lower half folds them into its own.
-          float* xm = xo + 64 * 128;
-          if (chalf == 1) {
-            ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x30a);
-            if (!ok) break;
+          // the lower / upper 32 columns of every tile).  Each half parks, in shared memory, the 64
+          // unnormalised O columns the OTHER half will store (16-byte chunks XOR-swizzled by row:
+          // conflict-free) with its maximum and row sum, then folds what the other half parked into
+          // the 64 columns it keeps: both halves merge, stage and store half a row.
+          float* xo = reinterpret_cast<float*>(sm + OFF_X);  // [half that stores][row][64 columns]
+          float* xm = xo + 2 * 64 * 64;                      // [half that wrote][row][m, l]
+          ok = wait_all(BAR(B_XFREE), (xcount & 1) ^ 1, abort_flag, 0x30a);  // the previous piece's is read
+          if (!ok) break;
+          float* park = xo + ((chalf ^ 1) * 64 + lrow) * 64;
+          if (chalf == 0) {
 #pragma unroll
-            for (int j = 0; j < kD / 4; ++j)
-              *reinterpret_cast<float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2)) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-            xm[2 * lrow] = m_used;
-            xm[2 * lrow + 1] = l;
-            mbar_arrive(BAR(B_XFULL));
+            for (int j = 0; j < 16; ++j)
+              *reinterpret_cast<float4*>(park + ((j ^ (lrow & 15)) << 2)) = make_float4(o[64 + 4 * j], o[65 + 4 * j], o[66 + 4 * j], o[67 + 4 * j]);
           } else {
-            ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x30b);
-            if (!ok) break;
-            const float m1 = xm[2 * lrow], l1 = xm[2 * lrow + 1];
-            const float mstar = fmaxf(m_used, m1);
-            const float w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
-            const float w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
 #pragma unroll
-            for (int j = 0; j < kD / 4; ++j) {
-              const float4 v = *reinterpret_cast<const float4*>(xo + lrow * 128 + ((j ^ (lrow & 31)) << 2));
+            for (int j = 0; j < 16; ++j)
+              *reinterpret_cast<float4*>(park + ((j ^ (lrow & 15)) << 2)) = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+          }
+          xm[(chalf * 64 + lrow) * 2] = m_used;
+          xm[(chalf * 64 + lrow) * 2 + 1] = l;
+          mbar_arrive(BAR(B_XFULL));
+          ok = wait_all(BAR(B_XFULL), xcount & 1, abort_flag, 0x30b);
+          if (!ok) break;
+          const float m1 = xm[((chalf ^ 1) * 64 + lrow) * 2], l1 = xm[((chalf ^ 1) * 64 + lrow) * 2 + 1];
+          const float mstar = fmaxf(m_used, m1);
+          const float w0 = m_used == -INFINITY ? 0.f : fta_exp2(m_used - mstar);
+          const float w1 = m1 == -INFINITY ? 0.f : fta_exp2(m1 - mstar);
+          const float* mine = xo + (chalf * 64 + lrow) * 64;
+          if (chalf == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float4 v = *reinterpret_cast<const float4*>(mine + ((j ^ (lrow & 15)) << 2));
               o[4 * j] = o[4 * j] * w0 + v.x * w1; o[4 * j + 1] = o[4 * j + 1] * w0 + v.y * w1;
               o[4 * j + 2] = o[4 * j + 2] * w0 + v.z * w1; o[4 * j + 3] = o[4 * j + 3] * w0 + v.w * w1;
             }
-            l = l * w0 + l1 * w1;
-            m_used = mstar;
-            mbar_arrive(BAR(B_XFREE));
+          } else {  // the kept columns 64..127 move down to o[0..63]
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float4 v = *reinterpret_cast<const float4*>(mine + ((j ^ (lrow & 15)) << 2));
+              o[4 * j] = o[64 + 4 * j] * w0 + v.x * w1; o[4 * j + 1] = o[65 + 4 * j] * w0 + v.y * w1;
+              o[4 * j + 2] = o[66 + 4 * j] * w0 + v.z * w1; o[4 * j + 3] = o[67 + 4 * j] * w0 + v.w * w1;
+            }
           }
+          l = l * w0 + l1 * w1;
+          m_used = mstar;
+          mbar_arrive(BAR(B_XFREE));
           ++xcount;
         }
 
         if (row == 0) FTA_TRACE_EP(8 + sidx, 0);
         if (p.split_mode == FTA_SPLIT_BALANCED && seg.split == 1 && row == 0)
           fta_cut_desc(p, g)[blockIdx.x] = make_int4(seg.b, seg.j, seg.nsplit, seg.p0slot);  // for stage 2
-        if (CS == 1 || chalf == 0) {  // uniform per warp: the upper half's warps have nothing to store
-          const bool rstore = rvalid;
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-          const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
-          const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
-          const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
-          void* dst;
-          int dt = FTA_DTYPE_F32;
-          long long off = 0;
-          if (final_direct) {
-            dst = p.out; dt = p.out_dtype;
-            if (rstore) {
-              off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
-              if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
+        if constexpr (CS == 1) {
+          {
+            const bool rstore = rvalid;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
+            const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
+            const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
+            void* dst;
+            int dt = FTA_DTYPE_F32;
+            long long off = 0;
+            if (final_direct) {
+              dst = p.out; dt = p.out_dtype;
+              if (rstore) {
+                off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
+                if (p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
+              }
+            } else if (p.split_mode == FTA_SPLIT_BALANCED) {
+              dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
+              if (rstore) ws_l[(long long)seg.slot * g.R + lrow] = lse;
+            } else if (tree_piece) {
+              dst = p.tree_o;
+              if (rstore) {
+                const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
+                off = ro * kD;
+                p.tree_lse[ro] = lse;
+              }
+            } else {
+              dst = p.mid_o;
+              if (rstore) {
+                off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
+                p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+              }
             }
-          } else if (p.split_mode == FTA_SPLIT_BALANCED) {
-            dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
-            if (rstore) ws_l[(long long)seg.slot * g.R + lrow] = lse;
-          } else if (tree_piece) {
-            dst = p.tree_o;
-            if (rstore) {
-              const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
-              off = ro * kD;
-              p.tree_lse[ro] = lse;
-            }
-          } else {
-            dst = p.mid_o;
-            if (rstore) {
-              off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
-              p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+            // The rows go through the Q buffer, this warp's own 32 rows of it, so that every store
+            // instruction of the warp writes two whole 256-byte row pieces: thread = row on the way in
+            // (16-byte chunks XOR-swizzled by row), 16 lanes per row on the way out.  fp32 rows take two
+            // passes of 64 columns, 16-bit rows one pass of 128.
+            if (row == 0) FTA_TRACE_EP(8 + sidx, 1);
+            const bool wide = dt == FTA_DTYPE_F32 ||
+                              (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((p.o_sb | p.o_sh | p.o_sq) & 7) == 0);
+            uint8_t* stg = sm + OFF_Q;
+            if (!wide) {
+              if (rstore) {
+  #pragma unroll
+                for (int c4 = 0; c4 < kD; c4 += 4)
+                  fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
+              }
+            } else {
+              const uint32_t esize = dt == FTA_DTYPE_F32 ? 4u : 2u;
+              const int c = lane & 15;
+  #pragma unroll
+              for (int pass = 0; pass < 2; ++pass) {
+                if (pass == 1 && dt != FTA_DTYPE_F32) break;
+                __syncwarp();  // the previous pass (or piece) has been read out
+                if (rstore) {
+  #pragma unroll
+                  for (int cc = 0; cc < 16; ++cc) {
+                    uint4 v;
+                    if (dt == FTA_DTYPE_F32) {
+                      const int e = pass * 64 + 4 * cc;
+                      v.x = __float_as_uint(o[e] * inv); v.y = __float_as_uint(o[e + 1] * inv);
+                      v.z = __float_as_uint(o[e + 2] * inv); v.w = __float_as_uint(o[e + 3] * inv);
+                    } else if (dt == FTA_DTYPE_F16) {
+                      const int e = 8 * cc;
+                      v.x = FtaType<__half>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__half>::pack(o[e + 2] * inv, o[e + 3] * inv);
+                      v.z = FtaType<__half>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__half>::pack(o[e + 6] * inv, o[e + 7] * inv);
+                    } else {
+                      const int e = 8 * cc;
+                      v.x = FtaType<__nv_bfloat16>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__nv_bfloat16>::pack(o[e + 2] * inv, o[e + 3] * inv);
+                      v.z = FtaType<__nv_bfloat16>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__nv_bfloat16>::pack(o[e + 6] * inv, o[e + 7] * inv);
+                    }
+                    *reinterpret_cast<uint4*>(stg + (cc >> 3) * kQHalf + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = v;
+                  }
+                }
+                if (row == 0) FTA_TRACE_EP(8 + sidx, 2 + 3 * pass);
+                __syncwarp();
+                uint8_t* gdst = reinterpret_cast<uint8_t*>(dst) + pass * 256 + c * 16;
+  #pragma unroll 4
+                for (int it = 0; it < 16; ++it) {
+                  const int rl = 2 * it + (lane >> 4);
+                  const int rr = quad * 32 + rl;
+                  const uint4 v = *reinterpret_cast<const uint4*>(stg + (c >> 3) * kQHalf + rr * 128 + (((c & 7) ^ (rr & 7)) << 4));
+                  const long long roff = __shfl_sync(0xffffffffu, off, rl);
+                  const bool rv = __shfl_sync(0xffffffffu, rstore ? 1 : 0, rl) != 0;
+                  if (rv) __stcg(reinterpret_cast<uint4*>(gdst + roff * esize), v);
+                }
+                if (row == 0) FTA_TRACE_EP(8 + sidx, 3 + 3 * pass);
+              }
+              __syncwarp();
+              if (row == 0) FTA_TRACE_EP(8 + sidx, 4);
             }
           }
-          // The rows go through the Q buffer, this warp's own 32 rows of it, so that every store
-          // instruction of the warp writes two whole 256-byte row pieces: thread = row on the way in
-          // (16-byte chunks XOR-swizzled by row), 16 lanes per row on the way out.  fp32 rows take two
-          // passes of 64 columns, 16-bit rows one pass of 128.
-          if (row == 0) FTA_TRACE_EP(8 + sidx, 1);
-          const bool wide = dt == FTA_DTYPE_F32 ||
-                            (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((p.o_sb | p.o_sh | p.o_sq) & 7) == 0);
-          uint8_t* stg = sm + OFF_Q;
-          if (!wide) {
-            if (rstore) {
-#pragma unroll
-              for (int c4 = 0; c4 < kD; c4 += 4)
-                fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
-            }
-          } else {
-            const uint32_t esize = dt == FTA_DTYPE_F32 ? 4u : 2u;
-            const int c = lane & 15;
-#pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
-              if (pass == 1 && dt != FTA_DTYPE_F32) break;
-              __syncwarp();  // the previous pass (or piece) has been read out
+        } else {
+          {
+            const bool rstore = rvalid;
+            const bool lstore = rvalid && chalf == 0;  // one thread per query row writes the LSE
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float lse = l > 0.f ? (m_used + fta_log2(l)) * FTA_LN2 : -INFINITY;
+            const bool final_direct = p.split_mode == FTA_SPLIT_BALANCED && seg.nsplit == 1;
+            const bool tree_piece = p.split_mode == FTA_SPLIT_FIXED && seg.split == g.fixed_max_splits;
+            void* dst;
+            int dt = FTA_DTYPE_F32;
+            long long off = 0;
+            if (final_direct) {
+              dst = p.out; dt = p.out_dtype;
               if (rstore) {
-#pragma unroll
-                for (int cc = 0; cc < 16; ++cc) {
-                  uint4 v;
-                  if (dt == FTA_DTYPE_F32) {
-                    const int e = pass * 64 + 4 * cc;
-                    v.x = __float_as_uint(o[e] * inv); v.y = __float_as_uint(o[e + 1] * inv);
-                    v.z = __float_as_uint(o[e + 2] * inv); v.w = __float_as_uint(o[e + 3] * inv);
-                  } else if (dt == FTA_DTYPE_F16) {
-                    const int e = 8 * cc;
-                    v.x = FtaType<__half>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__half>::pack(o[e + 2] * inv, o[e + 3] * inv);
-                    v.z = FtaType<__half>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__half>::pack(o[e + 6] * inv, o[e + 7] * inv);
-                  } else {
-                    const int e = 8 * cc;
-                    v.x = FtaType<__nv_bfloat16>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__nv_bfloat16>::pack(o[e + 2] * inv, o[e + 3] * inv);
-                    v.z = FtaType<__nv_bfloat16>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__nv_bfloat16>::pack(o[e + 6] * inv, o[e + 7] * inv);
-                  }
-                  *reinterpret_cast<uint4*>(stg + (cc >> 3) * kQHalf + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = v;
-                }
+                off = seg.b * p.o_sb + h * p.o_sh + qi * p.o_sq;
+                if (lstore && p.lse) p.lse[seg.b * p.l_sb + h * p.l_sh + qi] = lse;
               }
-              if (row == 0) FTA_TRACE_EP(8 + sidx, 2 + 3 * pass);
-              __syncwarp();
-              uint8_t* gdst = reinterpret_cast<uint8_t*>(dst) + pass * 256 + c * 16;
-#pragma unroll 4
-              for (int it = 0; it < 16; ++it) {
-                const int rl = 2 * it + (lane >> 4);
-                const int rr = quad * 32 + rl;
-                const uint4 v = *reinterpret_cast<const uint4*>(stg + (c >> 3) * kQHalf + rr * 128 + (((c & 7) ^ (rr & 7)) << 4));
-                const long long roff = __shfl_sync(0xffffffffu, off, rl);
-                const bool rv = __shfl_sync(0xffffffffu, rstore ? 1 : 0, rl) != 0;
-                if (rv) __stcg(reinterpret_cast<uint4*>(gdst + roff * esize), v);
+            } else if (p.split_mode == FTA_SPLIT_BALANCED) {
+              dst = ws_o; off = ((long long)seg.slot * g.R + lrow) * kD;
+              if (lstore) ws_l[(long long)seg.slot * g.R + lrow] = lse;
+            } else if (tree_piece) {
+              dst = p.tree_o;
+              if (rstore) {
+                const long long ro = ((long long)seg.b * p.H + h) * p.Q + qi;
+                off = ro * kD;
+                if (lstore) p.tree_lse[ro] = lse;
               }
-              if (row == 0) FTA_TRACE_EP(8 + sidx, 3 + 3 * pass);
+            } else {
+              dst = p.mid_o;
+              if (rstore) {
+                off = seg.b * p.mo_sb + h * p.mo_sh + seg.split * p.mo_ss + qi * p.mo_sq;
+                if (lstore) p.mid_lse[seg.b * p.ml_sb + h * p.ml_sh + seg.split * p.ml_ss + qi] = lse;
+              }
             }
-            __syncwarp();
-            if (row == 0) FTA_TRACE_EP(8 + sidx, 4);
+            off += col0;
+            // The row slices go through the Q buffer, each thread's own 128-byte lines of it, so that
+            // every store instruction of the warp writes whole row slices: thread = row on the way in
+            // (16-byte chunks XOR-swizzled by row), 8 or 16 lanes per row on the way out.  A pass moves
+            // up to 256 bytes per row; only full fp32 rows (512 bytes) take two.
+            if (row == 0) FTA_TRACE_EP(8 + sidx, 1);
+            const bool wide = dt == FTA_DTYPE_F32 ||
+                              (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && ((p.o_sb | p.o_sh | p.o_sq) & 7) == 0);
+            uint8_t* stg = sm + OFF_Q;
+            if (!wide) {
+              if (rstore) {
+  #pragma unroll
+                for (int c4 = 0; c4 < NCOL; c4 += 4)
+                  fta_store4(dst, dt, off + c4, make_float4(o[c4] * inv, o[c4 + 1] * inv, o[c4 + 2] * inv, o[c4 + 3] * inv));
+              }
+            } else {
+              const uint32_t esize = dt == FTA_DTYPE_F32 ? 4u : 2u;
+              const uint32_t slice = NCOL * esize;                 // bytes of a row this thread stores
+              const uint32_t pbytes = slice < 256u ? slice : 256u;  // per pass
+              const int npass = (int)(slice / pbytes);
+              const int lpr = CS == 1 ? 16 : (int)(pbytes / 16u);  // 16-byte chunks = lanes per row
+              const int c = lane & (lpr - 1), rsub = lane / lpr, rpi = 32 / lpr;
+  #pragma unroll
+              for (int pass = 0; pass < 2; ++pass) {
+                if (pass >= npass) break;
+                __syncwarp();  // the previous pass (or piece) has been read out
+                if (rstore) {
+  #pragma unroll
+                  for (int cc = 0; cc < 16; ++cc) {
+                    if (CS == 2 && cc >= lpr) break;
+                    uint4 v;
+                    if (dt == FTA_DTYPE_F32) {
+                      const int e = (pass * 64 + 4 * cc) % NCOL;
+                      v.x = __float_as_uint(o[e] * inv); v.y = __float_as_uint(o[e + 1] * inv);
+                      v.z = __float_as_uint(o[e + 2] * inv); v.w = __float_as_uint(o[e + 3] * inv);
+                    } else if (dt == FTA_DTYPE_F16) {
+                      const int e = (8 * cc) % NCOL;
+                      v.x = FtaType<__half>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__half>::pack(o[e + 2] * inv, o[e + 3] * inv);
+                      v.z = FtaType<__half>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__half>::pack(o[e + 6] * inv, o[e + 7] * inv);
+                    } else {
+                      const int e = (8 * cc) % NCOL;
+                      v.x = FtaType<__nv_bfloat16>::pack(o[e] * inv, o[e + 1] * inv); v.y = FtaType<__nv_bfloat16>::pack(o[e + 2] * inv, o[e + 3] * inv);
+                      v.z = FtaType<__nv_bfloat16>::pack(o[e + 4] * inv, o[e + 5] * inv); v.w = FtaType<__nv_bfloat16>::pack(o[e + 6] * inv, o[e + 7] * inv);
+                    }
+                    *reinterpret_cast<uint4*>(stg + (cc >> 3) * kQHalf + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = v;
+                  }
+                }
+                if (row == 0) FTA_TRACE_EP(8 + sidx, 2 + 3 * pass);
+                __syncwarp();
+                uint8_t* gdst = reinterpret_cast<uint8_t*>(dst) + pass * 256 + c * 16;
+  #pragma unroll 4
+                for (int it = 0; it < 16; ++it) {
+                  if (CS == 2 && it >= lpr) break;  // 32 rows, 32 / lpr of them per instruction
+                  const int rl = it * rpi + rsub;
+                  const int rr = quad * 32 + rl;
+                  const uint4 v = *reinterpret_cast<const uint4*>(stg + (c >> 3) * kQHalf + rr * 128 + (((c & 7) ^ (rr & 7)) << 4));
+                  const long long roff = __shfl_sync(0xffffffffu, off, rl);
+                  const bool rv = __shfl_sync(0xffffffffu, rstore ? 1 : 0, rl) != 0;
+                  if (rv) __stcg(reinterpret_cast<uint4*>(gdst + roff * esize), v);
+                }
+                if (row == 0) FTA_TRACE_EP(8 + sidx, 3 + 3 * pass);
+              }
+              __syncwarp();
+              if (row == 0) FTA_TRACE_EP(8 + sidx, 4);
+            }
           }
         }
       }
