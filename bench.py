@@ -444,7 +444,7 @@ def main():
             "metric": "tree_attn_calls_per_s", "value": calls_s, "unit": "calls/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": str(w.dtype).split(".")[-1].replace("float16", "fp16").replace("bfloat16", "bf16"),
+            "dtype": {"float16": "fp16", "bfloat16": "bf16"}.get(str(w.dtype).split(".")[-1], str(w.dtype)),
             "data": "synthetic", "config": workload_config(w, lens),
             "kv_read_gbs": all_kvb * args.steps / (ms * 1e-3) / 1e9,
             "kv_read_frac_of_measured_peak": all_kvb * args.steps / (ms * 1e-3) / 1e9 / (hbm_peak * world),
@@ -466,6 +466,14 @@ def main():
             line["e2e_cold"] = {"value": world * cold[1] / (cold[0] * 1e-3), "unit": "calls/s",
                                 "h2d_bytes_per_step": h2d + cache_bytes, "d2h_bytes_per_step": d2h,
                                 "note": "KV cache also copied from pinned host memory every step (PCIe-bound)"}
+        # G*Q query rows share every KV row: flops per KV byte = G*Q.  Above the ridge of the
+        # measured peaks the tensor pipe bounds the kernel, not HBM (cfg4: 512 flop/B).
+        fl = flops(w, lens)
+        if fl / kvb > tf_peak * 1e12 / (hbm_peak * 1e9):
+            ach_tf = fl / (ms_stage1 * 1e-3) / 1e12
+            line["roofline"].update({"bound": "tensor", "achieved": ach_tf, "peak": tf_peak, "unit": "TFLOP/s",
+                                     "frac": ach_tf / tf_peak, "algorithmic_flops_per_launch": fl,
+                                     "hbm_achieved_gbs": achieved})
         ratio = NCU_TRAFFIC_RATIO.get(args.workload)
         if ratio is not None and args.batch == 0:
             line["roofline"]["traffic"] = ratio[0] * kvb
