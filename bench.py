@@ -252,6 +252,9 @@ def main():
     ap.add_argument("--kernel", default=None, choices=[None, "auto", "mma", "umma"])
     ap.add_argument("--skip-e2e", action="store_true", help="device-timed region only (profiling runs)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch size (profiling runs)")
+    ap.add_argument("--paged", type=int, default=0, metavar="PAGE_SIZE",
+                    help="house the KV cache in shuffled pages of this many rows (multiple of 64) and "
+                         "run the device-timed region through the block table (implies --skip-e2e)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -294,7 +297,15 @@ def main():
     inp = make_inputs(wr, dev, lens=lens)
     call_args = (inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
                  inp["kv_seq_len"], w.block_size, w.ctx)
-    prep = fta.prepare(*call_args, kv_group_num=w.G)
+    if args.paged:
+        from flash_tree_attn_b200.workloads import to_paged
+        args.skip_e2e = True
+        kp, vp, table = to_paged(inp["k_cache"], inp["v_cache"], lens, page_size=args.paged, seed=wr.seed)
+        inp["k_cache"] = inp["v_cache"] = None  # the dense copy is not needed any more
+        prep = fta.prepare(inp["q"], kp, vp, inp["current_k"], inp["current_v"], inp["mask"], inp["kv_seq_len"],
+                           w.block_size, w.ctx, kv_group_num=w.G, block_table=table)
+    else:
+        prep = fta.prepare(*call_args, kv_group_num=w.G)
 
     def barrier():
         torch.cuda.synchronize()
@@ -412,7 +423,7 @@ def main():
         ms_e2e = e2e_region(args.steps)
 
     cold = None
-    cache_bytes = 2 * inp["k_cache"].numel() * inp["k_cache"].element_size()
+    cache_bytes = 0 if args.skip_e2e else 2 * inp["k_cache"].numel() * inp["k_cache"].element_size()
     if cache_bytes <= 8 << 30 and not args.skip_e2e:
         cold_host = (inp["k_cache"].cpu().pin_memory(), inp["v_cache"].cpu().pin_memory())
         n_cold = max(2, min(args.steps, 10))
@@ -445,7 +456,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"float16": "fp16", "bfloat16": "bf16"}.get(str(w.dtype).split(".")[-1], str(w.dtype)),
-            "data": "synthetic", "config": workload_config(w, lens),
+            "data": "synthetic",
+            "config": dict(workload_config(w, lens), **({"kv_cache": f"paged, {args.paged} rows per page, shuffled"} if args.paged else {})),
             "kv_read_gbs": all_kvb * args.steps / (ms * 1e-3) / 1e9,
             "kv_read_frac_of_measured_peak": all_kvb * args.steps / (ms * 1e-3) / 1e9 / (hbm_peak * world),
             "kv_read_frac_of_nominal_8tbs": all_kvb * args.steps / (ms * 1e-3) / 1e9 / (8000.0 * world),

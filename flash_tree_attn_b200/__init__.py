@@ -7,6 +7,7 @@ include/fta.h); build it with `python -m flash_tree_attn_b200.build`.
 """
 from .op import (  # noqa: F401
     flash_decoding_attention,
+    flash_decoding_attention_paged,
     flash_decoding_attention_with_lse,
     merge_partials,
     prepare,
@@ -17,6 +18,7 @@ from .op import (  # noqa: F401
 
 __all__ = [
     "flash_decoding_attention",
+    "flash_decoding_attention_paged",
     "flash_decoding_attention_with_lse",
     "merge_partials",
     "prepare",

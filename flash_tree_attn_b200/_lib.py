@@ -50,6 +50,7 @@ class FtaParams(C.Structure):
         ("dtype", _i32), ("out_dtype", _i32), ("sm_scale", _f32),
         ("split_mode", _i32), ("split_tokens", _i32), ("with_tree", _i32), ("kernel", _i32),
         ("grid_override", _i32), ("reserved_", _i32),
+        ("block_table", _vp), ("bt_sb", _i64), ("page_size", _i32), ("n_pages", _i32),
     ]
 
 

@@ -62,6 +62,11 @@ int validate(const FtaParams* p) {
     if (!mult(p->cv_sb, 8) || !mult(p->cv_sh, 8) || !mult(p->cv_st, 8)) return FTA_E_BADARG;
   }
   if (!aligned(p->out, 16) || !mult(p->o_sb, 4) || !mult(p->o_sh, 4) || !mult(p->o_sq, 4)) return FTA_E_BADARG;
+  if (p->block_table) {
+    // a 64-row tile never straddles two pages
+    if (p->page_size < FTA_TILE || p->page_size % FTA_TILE != 0 || p->n_pages < 1) return FTA_E_BADARG;
+    if (p->bt_sb < 0 || (long long)p->bt_sb * p->page_size < p->ctx) return FTA_E_BADARG;
+  }
   if (p->split_mode == FTA_SPLIT_BALANCED) {
     if (p->out_cache) return FTA_E_UNSUPPORTED;  // the cache-only result needs FIXED
     if (!p->workspace || !aligned(p->workspace, 16)) return FTA_E_WORKSPACE;

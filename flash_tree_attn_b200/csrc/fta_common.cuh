@@ -166,6 +166,26 @@ __host__ __device__ __forceinline__ bool fta_fixed_item(const FtaParams& p, cons
   return b < p.B;
 }
 
+// ---- cache addressing --------------------------------------------------------------------
+// Where cache rows [row0, row0 + 64) of sequence b start: for the dense cache (batch index b, row
+// row0), for a paged one (page from the block table, row within the page).  row0 is a multiple of
+// 64 and so is page_size, so a tile never straddles pages.
+struct FtaTileAt {
+  int batch;  // index along the cache's leading dimension
+  int row;    // first row within it
+};
+__device__ __forceinline__ FtaTileAt fta_tile_at(const FtaParams& p, int b, int row0) {
+  FtaTileAt t;
+  if (p.block_table == nullptr) {
+    t.batch = b; t.row = row0;
+  } else {
+    const int slot = row0 / p.page_size;
+    t.batch = __ldg(p.block_table + (long long)b * p.bt_sb + slot);
+    t.row = row0 - slot * p.page_size;
+  }
+  return t;
+}
+
 // ---- row <-> (head, query) mapping of an M tile -----------------------------------------
 struct FtaUnit {
   int kvh, gt, qt;  // KV head, group-tile, query-tile

@@ -175,8 +175,8 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
       mrow[e] = row_ok[e] ? p.mask + seg.b * p.m_sb + row_h[e] * p.m_sh + row_q[e] * p.m_sq : nullptr;
     }
 
-    const T* kbase = Kp + seg.b * p.k_sb + unit.kvh * p.k_sh;
-    const T* vbase = Vp + seg.b * p.v_sb + unit.kvh * p.v_sh;
+    const T* kbase = Kp + unit.kvh * p.k_sh;  // + the tile's batch / page and row
+    const T* vbase = Vp + unit.kvh * p.v_sh;
     const T* ckbase = CKp + seg.b * p.ck_sb + (long long)unit.kvh * p.cur_head_mul * p.ck_sh;
     const T* cvbase = CVp + seg.b * p.cv_sb + (long long)unit.kvh * p.cur_head_mul * p.cv_sh;
 
@@ -187,8 +187,9 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
         if (i < n_ct) {
           const int row0 = seg.c0 + i * FTA_TILE;
           const int valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
-          load_rows<T, D>(sK, kbase + (long long)row0 * p.k_st, p.k_st, valid);
-          load_rows<T, D>(sV, vbase + (long long)row0 * p.v_st, p.v_st, valid);
+          const FtaTileAt at = fta_tile_at(p, seg.b, row0);
+          load_rows<T, D>(sK, kbase + at.batch * p.k_sb + (long long)at.row * p.k_st, p.k_st, valid);
+          load_rows<T, D>(sV, vbase + at.batch * p.v_sb + (long long)at.row * p.v_st, p.v_st, valid);
         } else {
           const int row0 = (seg.tt0 + i - n_ct) * FTA_TILE;
           const int valid = p.Q - row0 < FTA_TILE ? p.Q - row0 : FTA_TILE;

@@ -305,16 +305,18 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
               if (i < 0 || i >= n) continue;
               const uint32_t t = gt + i, st = t % NS;
               const CUtensorMap* m;
-              int row0, head;
-              if (i < n_ct) { m = which == 0 ? &maps.k : &maps.v; row0 = seg.c0 + i * FTA_TILE; head = seg.kvh; }
-              else { m = which == 0 ? &maps.ck : &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = seg.kvh * p.cur_head_mul; }
+              int row0, head, bidx = seg.b;
+              if (i < n_ct) {
+                const FtaTileAt at = fta_tile_at(p, seg.b, seg.c0 + i * FTA_TILE);  // dense: (b, row); paged: (page, row in page)
+                m = which == 0 ? &maps.k : &maps.v; row0 = at.row; bidx = at.batch; head = seg.kvh;
+              } else { m = which == 0 ? &maps.ck : &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = seg.kvh * p.cur_head_mul; }
               const uint32_t full = BAR((which == 0 ? B_KFULL : B_VFULL) + st);
               ok = mbar_wait(BAR((which == 0 ? B_KEMPTY : B_VEMPTY) + st), ((t / NS) & 1) ^ 1, abort_flag, 0x102 + which);
               if (!ok) break;
               const uint32_t dst = base + OFF_RING + st * kStage + (which == 0 ? 0u : kKBytes);
               FTA_TRACE(t, which);
               mbar_expect_tx(full, kKBytes);
-              tma_load_5d(dst, m, full, 0, row0, head, 0, seg.b);
+              tma_load_5d(dst, m, full, 0, row0, head, 0, bidx);
             }
           }
           gt += n;
@@ -1128,7 +1130,8 @@ int fta_umma_supported(const FtaParams& p) {
   if (!stride_ok(p.q_sq) || !stride_ok(p.k_st) || !stride_ok(p.v_st)) return 0;
   if (p.H > 1 && !stride_ok(p.q_sh)) return 0;
   if (p.Hkv > 1 && (!stride_ok(p.k_sh) || !stride_ok(p.v_sh))) return 0;
-  if (p.B > 1 && (!stride_ok(p.q_sb) || !stride_ok(p.k_sb) || !stride_ok(p.v_sb))) return 0;
+  if (p.B > 1 && !stride_ok(p.q_sb)) return 0;
+  if ((p.block_table ? p.n_pages : p.B) > 1 && (!stride_ok(p.k_sb) || !stride_ok(p.v_sb))) return 0;
   if (p.with_tree) {
     if (!stride_ok(p.ck_st) || !stride_ok(p.cv_st)) return 0;
     if (p.Hkv * p.cur_head_mul > 1 && (!stride_ok(p.ck_sh) || !stride_ok(p.cv_sh))) return 0;
@@ -1172,9 +1175,12 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
 
   Maps maps;
   const int Hcur = p.Hkv * p.cur_head_mul;
+  // the cache as the copy engine sees it: [B, Hkv, ctx, D], or a pool of pages [n_pages, Hkv, page_size, D]
+  const uint64_t crows = p.block_table ? (uint64_t)p.page_size : (uint64_t)p.ctx;
+  const uint64_t cbatch = p.block_table ? (uint64_t)p.n_pages : (uint64_t)p.B;
   bool ok = make_map(&maps.q, p.q, p.dtype, p.Q, p.H, p.B, p.q_sq, p.q_sh, p.q_sb, g.qpt, g.hpt, false) &&
-            make_map(&maps.k, p.k_cache, p.dtype, p.ctx, p.Hkv, p.B, p.k_st, p.k_sh, p.k_sb, FTA_TILE, 1, true) &&
-            make_map(&maps.v, p.v_cache, p.dtype, p.ctx, p.Hkv, p.B, p.v_st, p.v_sh, p.v_sb, FTA_TILE, 1, true);
+            make_map(&maps.k, p.k_cache, p.dtype, crows, p.Hkv, cbatch, p.k_st, p.k_sh, p.k_sb, FTA_TILE, 1, true) &&
+            make_map(&maps.v, p.v_cache, p.dtype, crows, p.Hkv, cbatch, p.v_st, p.v_sh, p.v_sb, FTA_TILE, 1, true);
   if (ok && p.with_tree) {
     ok = make_map(&maps.ck, p.cur_k, p.dtype, p.Q, Hcur, p.B, p.ck_st, p.ck_sh, p.ck_sb, FTA_TILE, 1, true) &&
          make_map(&maps.cv, p.cur_v, p.dtype, p.Q, Hcur, p.B, p.cv_st, p.cv_sh, p.cv_sb, FTA_TILE, 1, true);

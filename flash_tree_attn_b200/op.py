@@ -115,10 +115,11 @@ class PreparedCall:
 def prepare(
     q, k_cache, v_cache, current_k, current_v, mask, kv_seq_len, block_size=64, max_seq_len_in_batch=None,
     output=None, mid_output=None, mid_output_lse=None, sm_scale=None, kv_group_num=1, *,
-    want_lse=False, out_dtype=None, with_tree=True, out_buf=None, lse_buf=None,
+    want_lse=False, out_dtype=None, with_tree=True, out_buf=None, lse_buf=None, block_table=None,
 ) -> PreparedCall:
     """Validate the arguments of flash_decoding_attention and build the C-ABI call without
-    launching it."""
+    launching it.  With `block_table` [bsz, max_pages] int32 the caches are pools of pages
+    [n_pages, num_kv_heads, page_size, head_dim] (see flash_decoding_attention_paged)."""
     lib = _lib.load()
     if not q.is_cuda:
         raise RuntimeError("flash_decoding_attention runs on CUDA tensors only (no CPU path exists)")
@@ -134,10 +135,18 @@ def prepare(
     G = int(kv_group_num)
     assert G >= 1 and H % G == 0, "num_heads must be a multiple of kv_group_num"
     Hkv = H // G
-    assert k_cache.size(0) >= B and k_cache.size(1) == Hkv, "k_cache must be [bsz, num_kv_heads, ctx, head_dim]"
+    paged = block_table is not None
+    if paged:
+        assert k_cache.size(1) == Hkv and tuple(k_cache.shape) == tuple(v_cache.shape), \
+            "paged caches must be [n_pages, num_kv_heads, page_size, head_dim]"
+        page_size = int(k_cache.size(-2))
+        assert page_size % 64 == 0, "page_size must be a multiple of 64"
+        assert block_table.dim() == 2 and block_table.size(0) == B, "block_table must be [bsz, max_pages]"
+    else:
+        assert k_cache.size(0) >= B and k_cache.size(1) == Hkv, "k_cache must be [bsz, num_kv_heads, ctx, head_dim]"
 
     sm_scale = 1.0 / (D ** 0.5) if sm_scale is None else float(sm_scale)
-    ctx = int(k_cache.size(-2))
+    ctx = int(block_table.size(1)) * page_size if paged else int(k_cache.size(-2))
     if max_seq_len_in_batch is not None:
         ctx = min(ctx, int(max_seq_len_in_batch))
     # For compatibility with the reference's buffer contract (flash_tree_attn.py:274)
@@ -177,6 +186,12 @@ def prepare(
     p.len_is_i64 = 1 if kv_seq_len.dtype == torch.int64 else 0
     p.cur_head_mul = 1
     keep = [q, k_cache, v_cache, kv_seq_len]
+    if paged:
+        if block_table.dtype != torch.int32 or not block_table.is_contiguous() or block_table.device != dev:
+            block_table = block_table.to(device=dev, dtype=torch.int32).contiguous()
+        p.block_table = block_table.data_ptr(); p.bt_sb = block_table.stride(0)
+        p.page_size = page_size; p.n_pages = int(k_cache.size(0))
+        keep.append(block_table)
 
     if with_tree:
         assert current_k.dtype == q.dtype and current_v.dtype == q.dtype
@@ -331,6 +346,33 @@ def flash_decoding_attention(
         want_lse=False, out_dtype=None, with_tree=True,
     )
     return out
+
+
+def flash_decoding_attention_paged(
+    q, k_pages, v_pages, block_table, current_k, current_v, mask, kv_seq_len, max_seq_len_in_batch=None,
+    sm_scale=None, kv_group_num=1, *, return_lse: bool = False,
+):
+    """The same operator over a paged KV cache, the layout the reference's docstring announces
+    (flash_tree_attn.py:233) and its README lists as to do, while its kernels index a dense padded
+    cache (:72-73).
+
+    Args:
+        k_pages, v_pages: [n_pages, num_kv_heads, page_size, head_dim] pools of pages shared by all
+            sequences; page_size a multiple of 64.
+        block_table: [bsz, max_pages] int32; row r of sequence b is row r % page_size of page
+            block_table[b, r // page_size].  Entries past ceil(kv_seq_len[b] / page_size) are
+            never read.
+        others: as flash_decoding_attention.
+
+    Returns the attention [bsz, num_heads, q_len, head_dim] (and the fp32 LSE if `return_lse`).
+    Nothing is gathered or copied: the stage-1 kernels look the page of every 64-row tile up.
+    """
+    out, lse = _decode(
+        q, k_pages, v_pages, current_k, current_v, mask, kv_seq_len, 64, max_seq_len_in_batch,
+        None, None, None, sm_scale, kv_group_num,
+        want_lse=return_lse, out_dtype=None, with_tree=True, block_table=block_table,
+    )
+    return (out, lse) if return_lse else out
 
 
 def flash_decoding_attention_with_lse(

@@ -121,6 +121,18 @@ typedef struct FtaParams {
   int32_t kernel;       /* FTA_KERNEL_* */
   int32_t grid_override; /* 0 = planner's choice; else resident blocks to launch (tests) */
   int32_t reserved_;
+
+  /* Paged cache (optional; block_table == NULL selects the dense cache above).  k_cache / v_cache
+     are then pools of pages [n_pages, Hkv, page_size, D] (k_sb / v_sb = page stride, k_sh, k_st as
+     before) and row r of sequence b lives in page block_table[b * bt_sb + r / page_size] at row
+     r % page_size.  page_size is a multiple of 64; ctx is the largest kv_seq_len the table can
+     hold, i.e. at most bt_sb * page_size.  The reference's docstring announces such a cache
+     (flash_tree_attn.py:233) but its kernels index a dense padded one (:72-73); this is the layout
+     its README lists as to do. */
+  const int32_t* block_table;
+  int64_t bt_sb;
+  int32_t page_size;
+  int32_t n_pages;
 } FtaParams;
 
 /*

@@ -35,7 +35,7 @@ def test_version_and_strerror(fta_lib):
 
 def test_struct_layout_matches_header():
     # sizes printed by a C++ compile of include/fta.h
-    assert C.sizeof(_lib.FtaParams) == 472
+    assert C.sizeof(_lib.FtaParams) == 496
     assert C.sizeof(_lib.FtaMergeParams) == 64
 
 
