@@ -59,6 +59,53 @@ def test_decode_rejects_bad_arguments(fta_lib):
     assert fta_lib.fta_decode(None, None) == _lib.FTA_E_BADARG
 
 
+def test_paged_cache_arguments_are_validated(fta_lib):
+    """Pointers here are fake but aligned: validation ends before anything is dereferenced or
+    launched.  A page must hold whole 64-row tiles and the table must cover ctx."""
+    def base():
+        p = _params(2, 8, 8, 8, 64, 256, 4, with_tree=0)
+        p.split_mode = _lib.SPLIT_BALANCED
+        for name in ("q", "k_cache", "v_cache", "kv_seq_len", "out", "workspace"):
+            setattr(p, name, 4096)
+        for name in ("q_sb", "q_sh", "q_sq", "k_sb", "k_sh", "k_st", "v_sb", "v_sh", "v_st", "o_sb", "o_sh", "o_sq"):
+            setattr(p, name, 64)
+        p.block_table = 4096
+        p.n_pages = 16
+        return p
+
+    p = base(); p.page_size = 32; p.bt_sb = 8   # smaller than a tile
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+    p = base(); p.page_size = 96; p.bt_sb = 8   # not a multiple of 64
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+    p = base(); p.page_size = 64; p.bt_sb = 3   # 3 pages of 64 rows cannot hold ctx = 256
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+    p = base(); p.page_size = 64; p.bt_sb = 4; p.n_pages = 0
+    assert fta_lib.fta_decode(C.byref(p), None) == _lib.FTA_E_BADARG
+
+
+def test_pages_hold_the_dense_rows():
+    """workloads.to_paged (used by the GPU tests and bench.py --paged): reading the pages back
+    through the table gives the dense rows below each length; everything else in the pool is NaN."""
+    import torch
+    from flash_tree_attn_b200.workloads import to_paged
+
+    torch.manual_seed(3)
+    lens = [130, 0, 64, 1]
+    k = torch.randn(4, 2, 192, 32).half()
+    v = torch.randn(4, 2, 192, 32).half()
+    for page in (64, 128):
+        kp, vp, table = to_paged(k, v, lens, page_size=page, seed=7)
+        used = set()
+        for b, L in enumerate(lens):
+            for r in range(L):
+                pg = int(table[b, r // page])
+                used.add(pg)
+                assert torch.equal(kp[pg, :, r % page], k[b, :, r]) and torch.equal(vp[pg, :, r % page], v[b, :, r])
+        assert len(used) == sum(-(-L // page) for L in lens)
+        finite = torch.isfinite(kp.float()).all(dim=-1).all(dim=1)  # [n_pages, page]
+        assert int(finite.sum()) == sum(lens)
+
+
 def plan(fta_lib, lens, H, Hkv, Q, D, grid, with_tree=1):
     B = len(lens)
     p = _params(B, H, Hkv, Q, D, max(lens + [1]), grid, with_tree)
