@@ -132,39 +132,12 @@ struct FtaBalanced {
     if (total + per < 0x7fffffffLL) return segment_at_t<unsigned int>(c, (unsigned int)lin, s);
     return segment_at_t<long long>(c, lin, s);
   }
-
-  // For the merge: pieces of unit (b, j) and the slot of piece i.
-  __host__ __device__ int unit_pieces(int b, int j, int& cfirst, long long& ustart) const {
-    const int ut = pre[b + 1] - pre[b];
-    if (ut == 0) { cfirst = 0; ustart = 0; return 0; }
-    ustart = (long long)U * pre[b] + (long long)j * ut;
-    const long long uend = ustart + ut - pad;  // end of the real tiles
-    cfirst = (int)(ustart / per);
-    return (int)((uend - 1) / per) - cfirst + 1;
-  }
-  __host__ __device__ int piece_slot(int cfirst, long long ustart, int i) const {
-    const int c = cfirst + i;
-    // piece i>0 starts exactly at block c's first tile; piece 0 does so only when the
-    // unit itself starts there
-    const bool first_of_block = (i > 0) || (ustart == (long long)c * per);
-    return 2 * c + (first_of_block ? 0 : 1);
-  }
 };
 
 // ---- FIXED plan ------------------------------------------------------------------------
-// Items are (b, j, s), s in [0, fixed_max_splits] ; s < ceil(L_b/split_tokens) is a cache
-// split, s == fixed_max_splits is the tree piece.  Items are dealt round-robin.
-__host__ __device__ __forceinline__ bool fta_fixed_item(const FtaParams& p, const FtaGeom& g,
-                                                        long long item, int L_of_b_plus1_unused,
-                                                        int& b, int& j, int& s) {
-  const int per_unit = g.fixed_max_splits + 1;
-  const long long per_b = (long long)g.U * per_unit;
-  b = (int)(item / per_b);
-  const long long r = item - (long long)b * per_b;
-  j = (int)(r / per_unit);
-  s = (int)(r - (long long)j * per_unit);
-  return b < p.B;
-}
+// Items are (b, j, s), s in [0, fixed_max_splits]; s < ceil(L_b/split_tokens) is a cache split,
+// s == fixed_max_splits is the tree piece.  Items are dealt round-robin to the blocks (the walk
+// is in each stage-1 kernel).
 
 // ---- cache addressing --------------------------------------------------------------------
 // Where cache rows [row0, row0 + 64) of sequence b start: for the dense cache (batch index b, row

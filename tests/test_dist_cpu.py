@@ -64,7 +64,7 @@ def _worker(rank, world, port, fail_rank, ret):
 
 def _run(world, fail_rank=-1):
     port = _free_port()
-    ret = mp.Manager().dict()
+    ret = mp.get_context("spawn").Manager().dict()
     mp.spawn(_worker, args=(world, port, fail_rank, ret), nprocs=world, join=True)
     return dict(ret)
 
