@@ -6,6 +6,7 @@ The arithmetic lives in libfta.so (hand-written sm_100a CUDA behind the C ABI of
 include/fta.h); build it with `python -m flash_tree_attn_b200.build`.
 """
 from .op import (  # noqa: F401
+    commit_accepted,
     flash_decoding_attention,
     flash_decoding_attention_paged,
     flash_decoding_attention_with_lse,
@@ -17,6 +18,7 @@ from .op import (  # noqa: F401
 )
 
 __all__ = [
+    "commit_accepted",
     "flash_decoding_attention",
     "flash_decoding_attention_paged",
     "flash_decoding_attention_with_lse",

@@ -65,6 +65,22 @@ class FtaMergeParams(C.Structure):
     ]
 
 
+class FtaCommitParams(C.Structure):
+    """Mirror of `struct FtaCommitParams` (include/fta.h)."""
+
+    _fields_ = [
+        ("cur_k", _vp), ("ck_sb", _i64), ("ck_sh", _i64), ("ck_st", _i64),
+        ("cur_v", _vp), ("cv_sb", _i64), ("cv_sh", _i64), ("cv_st", _i64),
+        ("k_cache", _vp), ("k_sb", _i64), ("k_sh", _i64), ("k_st", _i64),
+        ("v_cache", _vp), ("v_sb", _i64), ("v_sh", _i64), ("v_st", _i64),
+        ("accept_idx", _vp), ("ai_sb", _i64),
+        ("accept_len", _vp), ("kv_seq_len", _vp),
+        ("block_table", _vp), ("bt_sb", _i64),
+        ("len_is_i64", _i32), ("cur_head_mul", _i32), ("page_size", _i32), ("n_pages", _i32),
+        ("B", _i32), ("Hkv", _i32), ("Q", _i32), ("D", _i32), ("ctx", _i32), ("max_accept", _i32),
+    ]
+
+
 # every symbol include/fta.h declares: (restype, argtypes)
 SYMBOLS = {
     "fta_version": (C.c_int, []),
@@ -77,6 +93,7 @@ SYMBOLS = {
     "fta_stage1": (C.c_int, [C.POINTER(FtaParams), _vp]),
     "fta_stage2": (C.c_int, [C.POINTER(FtaParams), _vp]),
     "fta_merge_parts": (C.c_int, [C.POINTER(FtaMergeParams), _vp]),
+    "fta_commit_accepted": (C.c_int, [C.POINTER(FtaCommitParams), _vp]),
     "fta_plan_host": (_i64, [C.POINTER(FtaParams), C.POINTER(_i64), C.POINTER(_i64), _i64,
                              C.POINTER(_i32), C.POINTER(_i32)]),
     "fta_plan_grid": (C.c_int, [C.POINTER(FtaParams)]),

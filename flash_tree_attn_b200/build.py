@@ -21,6 +21,7 @@ LIB = os.path.join(HERE, "libfta.so")
 SOURCES = [
     "fta_api.cu",
     "fta_stage2.cu",
+    "fta_commit.cu",
     "fta_stage1_umma.cu",
     "fta_stage1_mma_d32.cu",
     "fta_stage1_mma_d64.cu",

@@ -16,6 +16,7 @@ cudaError_t fta_launch_stage1_mma_d256(const FtaParams&, const FtaGeom&, cudaStr
 cudaError_t fta_launch_stage1_umma(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*);
 int fta_umma_supported(const FtaParams&);
 cudaError_t fta_launch_stage2(const FtaParams&, const FtaGeom&, cudaStream_t);
+cudaError_t fta_launch_commit(const FtaCommitParams&, cudaStream_t);
 cudaError_t fta_launch_merge_parts(const FtaMergeParams&, cudaStream_t);
 
 // Scratch of fta_decode_static: partial results of the BALANCED plan live here instead of in a
@@ -289,6 +290,22 @@ int fta_merge_parts(const FtaMergeParams* p, void* stream) {
   if (p->out_dtype < FTA_DTYPE_F16 || p->out_dtype > FTA_DTYPE_F32) return FTA_E_BADARG;
   if (p->rows == 0) return FTA_OK;
   cudaError_t e = fta_launch_merge_parts(*p, (cudaStream_t)stream);
+  return e == cudaSuccess ? FTA_OK : cuda_fail(e);
+}
+
+int fta_commit_accepted(const FtaCommitParams* p, void* stream) {
+  if (!p || !p->cur_k || !p->cur_v || !p->k_cache || !p->v_cache || !p->accept_idx || !p->accept_len || !p->kv_seq_len)
+    return FTA_E_BADARG;
+  if (p->B <= 0 || p->Hkv <= 0 || p->Q <= 0 || p->ctx <= 0 || p->max_accept < 0 || p->cur_head_mul < 1) return FTA_E_BADARG;
+  if (p->D <= 0 || p->D % 8 != 0) return FTA_E_BADARG;
+  if (!aligned(p->cur_k, 16) || !aligned(p->cur_v, 16) || !aligned(p->k_cache, 16) || !aligned(p->v_cache, 16)) return FTA_E_BADARG;
+  if (!mult(p->ck_sb, 8) || !mult(p->ck_sh, 8) || !mult(p->ck_st, 8) || !mult(p->cv_sb, 8) || !mult(p->cv_sh, 8) || !mult(p->cv_st, 8))
+    return FTA_E_BADARG;
+  if (!mult(p->k_sb, 8) || !mult(p->k_sh, 8) || !mult(p->k_st, 8) || !mult(p->v_sb, 8) || !mult(p->v_sh, 8) || !mult(p->v_st, 8))
+    return FTA_E_BADARG;
+  if (p->block_table && (p->page_size < 1 || p->n_pages < 1 || (long long)p->bt_sb * p->page_size < p->ctx)) return FTA_E_BADARG;
+  if (p->max_accept == 0) return FTA_OK;
+  cudaError_t e = fta_launch_commit(*p, (cudaStream_t)stream);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 

@@ -395,6 +395,73 @@ def flash_decoding_attention_with_lse(
     )
 
 
+def commit_accepted(k_cache, v_cache, current_k, current_v, kv_seq_len, accept_idx, accept_len, *,
+                    kv_group_num: int = 1, block_table: Optional[torch.Tensor] = None) -> None:
+    """The step after the operator in a speculative-decoding loop: append the accepted tree nodes'
+    keys and values to the cache, in place, and grow `kv_seq_len`, in place.
+
+    Args:
+        k_cache, v_cache: the caches the operator read (dense [bsz, num_kv_heads, ctx, head_dim],
+            or pools of pages with `block_table`), updated in place.
+        current_k, current_v: the tree nodes' keys/values as given to the operator.
+        kv_seq_len: [bsz] int32/int64 on the device, updated in place (+= accept_len, at most ctx).
+        accept_idx: [bsz, max_accept] int32 tree-node indices in path order.
+        accept_len: [bsz] int32 number of accepted nodes per sequence.
+
+    Node accept_idx[b, i] becomes cache row kv_seq_len[b] + i.  Asynchronous on the current stream,
+    no host synchronisation.  The reference has no such step (its tree tokens stay outside the
+    cache, README), so this follows the rule stated in include/fta.h only.
+    """
+    lib = _lib.load()
+    assert k_cache.is_cuda and kv_seq_len.is_cuda, "commit_accepted runs on CUDA tensors only"
+    assert k_cache.dtype == v_cache.dtype == current_k.dtype == current_v.dtype
+    assert k_cache.dtype in (torch.float16, torch.bfloat16)
+    assert _rows_ok(k_cache) and _rows_ok(v_cache), "caches are updated in place and must have 16-byte rows"
+    assert kv_seq_len.dtype in (torch.int32, torch.int64) and kv_seq_len.is_contiguous()
+    dev = k_cache.device
+    B = kv_seq_len.numel()
+    Hkv, D = int(k_cache.size(1)), int(k_cache.size(3))
+    hk, Q = int(current_k.size(1)), int(current_k.size(2))
+    G = int(kv_group_num)
+    assert hk in (Hkv, Hkv * G) and current_v.size(1) == hk
+    if not _rows_ok(current_k):
+        current_k = current_k.contiguous()
+    if not _rows_ok(current_v):
+        current_v = current_v.contiguous()
+    accept_idx = accept_idx.to(device=dev, dtype=torch.int32)
+    if accept_idx.stride(-1) != 1:
+        accept_idx = accept_idx.contiguous()
+    accept_len = accept_len.to(device=dev, dtype=torch.int32).contiguous()
+    assert accept_idx.dim() == 2 and accept_idx.size(0) == B and accept_len.numel() == B
+
+    p = _lib.FtaCommitParams()
+    p.cur_k = current_k.data_ptr(); p.ck_sb, p.ck_sh, p.ck_st = current_k.stride(0), current_k.stride(1), current_k.stride(2)
+    p.cur_v = current_v.data_ptr(); p.cv_sb, p.cv_sh, p.cv_st = current_v.stride(0), current_v.stride(1), current_v.stride(2)
+    p.k_cache = k_cache.data_ptr(); p.k_sb, p.k_sh, p.k_st = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+    p.v_cache = v_cache.data_ptr(); p.v_sb, p.v_sh, p.v_st = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
+    p.accept_idx = accept_idx.data_ptr(); p.ai_sb = accept_idx.stride(0)
+    p.accept_len = accept_len.data_ptr()
+    p.kv_seq_len = kv_seq_len.data_ptr()
+    p.len_is_i64 = 1 if kv_seq_len.dtype == torch.int64 else 0
+    p.cur_head_mul = G if (hk == Hkv * G and G > 1) else 1
+    keep = [accept_idx, accept_len, current_k, current_v]
+    if block_table is not None:
+        if block_table.dtype != torch.int32 or not block_table.is_contiguous() or block_table.device != dev:
+            block_table = block_table.to(device=dev, dtype=torch.int32).contiguous()
+        p.block_table = block_table.data_ptr(); p.bt_sb = block_table.stride(0)
+        p.page_size = int(k_cache.size(2)); p.n_pages = int(k_cache.size(0))
+        p.ctx = int(block_table.size(1)) * p.page_size
+        keep.append(block_table)
+    else:
+        assert k_cache.size(0) >= B
+        p.ctx = int(k_cache.size(2))
+    p.B, p.Hkv, p.Q, p.D, p.max_accept = B, Hkv, Q, D, int(accept_idx.size(1))
+    _lib.check(lib.fta_commit_accepted(C.byref(p), torch.cuda.current_stream(dev).cuda_stream), "fta_commit_accepted")
+    # the temporaries above are read by the kernels after this returns: tie them to the stream
+    for t in keep:
+        t.record_stream(torch.cuda.current_stream(dev))
+
+
 def merge_partials(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype: torch.dtype = torch.float32):
     """LSE-merge n normalised partial attentions: part_o [n, rows.., D] fp32, part_lse
     [n, rows..] fp32 -> (out [rows.., D], lse [rows..]).  Used after the all-gather of

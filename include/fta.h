@@ -158,6 +158,41 @@ typedef struct FtaMergeParams {
 /* Library / ABI version (FTA_VERSION).  No counterpart in the reference. */
 int fta_version(void);
 
+/*
+ * Accept/commit, the step after the operator in a speculative-decoding loop: append the accepted
+ * tree nodes' keys and values to the cache and grow the lengths.  No counterpart in the reference,
+ * which keeps the tree tokens outside the cache (README: "not yet in the cache") and ends there.
+ *   cur_k / cur_v   [B, Hkv * cur_head_mul, Q, D] as given to the operator (16-bit elements)
+ *   k_cache/v_cache dense [B, Hkv, ctx, D], or pools of pages with block_table as in FtaParams
+ *   accept_idx      [B, max_accept] int32, tree-node indices in path order (row stride ai_sb)
+ *   accept_len      [B] int32, how many of them count
+ *   kv_seq_len      [B] int32/int64, updated in place: += accept_len[b], saturating at ctx
+ * Node i of sequence b lands in cache row kv_seq_len[b] + i; rows at or past ctx are dropped.
+ */
+typedef struct FtaCommitParams {
+  const void* cur_k;
+  int64_t ck_sb, ck_sh, ck_st;
+  const void* cur_v;
+  int64_t cv_sb, cv_sh, cv_st;
+  void* k_cache;
+  int64_t k_sb, k_sh, k_st;
+  void* v_cache;
+  int64_t v_sb, v_sh, v_st;
+  const int32_t* accept_idx;
+  int64_t ai_sb;
+  const int32_t* accept_len;
+  void* kv_seq_len;
+  const int32_t* block_table;
+  int64_t bt_sb;
+  int32_t len_is_i64;
+  int32_t cur_head_mul;
+  int32_t page_size;
+  int32_t n_pages;
+  int32_t B, Hkv, Q, D, ctx, max_accept;
+} FtaCommitParams;
+
+int fta_commit_accepted(const FtaCommitParams* p, void* stream);
+
 /* Text for an FTA_E_* code.  No counterpart in the reference (it raises AssertionError,
    flash_tree_attn.py:263-291). */
 const char* fta_strerror(int code);
