@@ -356,3 +356,28 @@ def test_kv_range_shards_merge_to_whole(fta):
         parts_l.append(l)
     out, lse = fta.merge_partials(torch.stack(parts_o), torch.stack(parts_l), torch.bfloat16)
     _check(out, lse, ora, "kv-range shards")
+
+
+def test_call_is_capturable_in_a_cuda_graph_and_follows_the_lengths(fta):
+    """A prepared call neither allocates nor synchronises, and it builds its plan on the device from
+    kv_seq_len: captured once in a CUDA graph, it gives the right answer on every replay even after
+    q and the lengths have been changed in place (the reference reads the lengths back with .item(),
+    flash_tree_attn.py:272, which a capture cannot contain)."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel("auto")
+    w = _workload(B=3, H=8, G=2, D=128, Q=32, ctx=2048, lens="fixed:2048,900,3")
+    inp = make_inputs(w, "cuda")
+    args = (inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"], inp["kv_seq_len"], 64, 2048)
+    fta.prepare(*args, kv_group_num=2, want_lse=True).run()  # first launch outside the capture: tensor maps, function attributes
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        # the capture runs on its own stream: prepare there so that the call is issued on it
+        out, lse = fta.prepare(*args, kv_group_num=2, want_lse=True).run()
+    for lens in ([2048, 900, 3], [5, 2047, 1111], [64, 0, 2048]):
+        inp["kv_seq_len"].copy_(torch.tensor(lens, dtype=inp["kv_seq_len"].dtype))
+        inp["q"].normal_()
+        graph.replay()
+        torch.cuda.synchronize()
+        _check(out, lse, _oracle(inp, 2), f"graph replay lens={lens}")
