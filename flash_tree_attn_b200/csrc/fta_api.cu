@@ -153,6 +153,8 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
   // measured cost of ending a unit, in tile times of the family's steady state
   g.pad = (fam == FTA_KERNEL_UMMA && g.cs == 2) ? 8 : 4;
   g.grid = p.grid_override > 0 ? p.grid_override : 1;
+  // M tiles of one KV head walk the same tiles in neighbouring blocks (FtaBalanced: lanes)
+  g.lanes = (g.mtiles > 1 && g.grid >= g.mtiles) ? g.mtiles : 1;
   if (!need_grid || p.grid_override > 0) return FTA_OK;
 
   int dev; DevInfo* di;
@@ -168,6 +170,7 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
     occ = o;
   }
   g.grid = di->sms * occ;
+  g.lanes = (g.mtiles > 1 && g.grid >= g.mtiles) ? g.mtiles : 1;
   return FTA_OK;
 }
 
@@ -324,15 +327,13 @@ int64_t fta_plan_host(const FtaParams* p, const int64_t* lens, int64_t* segs_out
     pre[b + 1] = pre[b] + fta_unit_tiles(L, g.n_tree, g.pad);
   }
   FtaBalanced plan;
-  plan.pre = pre.data(); plan.B = q.B; plan.U = g.U; plan.n_tree = g.n_tree; plan.pad = g.pad;
-  plan.total = (long long)g.U * pre[q.B];
-  plan.per = FtaBalanced::choose_per(plan.total, g.grid, g.min_per);
+  plan.init(pre.data(), q.B, g, g.grid);
   if (grid_out) *grid_out = g.grid;
   if (per_out) *per_out = plan.per;
   int64_t n = 0;
   for (int c = 0; c < g.grid; ++c) {
-    long long lin = (long long)c * plan.per;
-    const long long end = lin + plan.per < plan.total ? lin + plan.per : plan.total;
+    long long lin = 0, end = 0;
+    if (!plan.range(c, g.grid, lin, end)) continue;
     while (lin < end) {
       FtaSeg s;
       lin = plan.segment_at(c, lin, s);

@@ -33,6 +33,7 @@ struct FtaGeom {
   int family;  // FTA_KERNEL_MMA or FTA_KERNEL_UMMA
   int cs;      // tcgen05 family: column split (2 when a unit has at most 64 query rows, else 1)
   int pad;     // BALANCED: what ending a unit costs a block, in tiles (see FtaBalanced)
+  int lanes;   // BALANCED: blocks that walk the same tiles side by side, one M tile each (see FtaBalanced)
 };
 
 // One contiguous piece of one unit, processed by one block without interruption.
@@ -65,6 +66,14 @@ __host__ __device__ __forceinline__ int fta_load_len(const void* lens, int is_i6
 // starts at U*pre[b] + j*ut_b.  Block c owns the line positions [c*per, (c+1)*per), so blocks that
 // end more units get fewer real tiles.  A unit whose real tiles are cut by k block boundaries has
 // k+1 pieces; a range that covers only virtual tiles of a unit gives an empty piece, which callers skip.
+//
+// Lanes.  When a KV head's query rows need several M tiles (G*Q > rows of a tile), those units read
+// the same K/V rows.  They are then not laid one after the other: the line holds one entry per KV
+// head, `lanes` = M tiles per KV head, and blocks come in groups of `lanes` that own the same line
+// range, block c working for M tile c % lanes.  The blocks of a group start together and walk the
+// same tiles at the same pace, so all but the first request of a tile are served by L2 instead of
+// DRAM.  Slots, pieces and cut descriptors stay per block; the pieces of one unit now sit `lanes`
+// blocks apart.
 __host__ __device__ __forceinline__ int fta_unit_tiles(int L, int n_tree, int pad) {
   const int real = (L + FTA_TILE - 1) / FTA_TILE + n_tree;
   return real > 0 ? real + pad : 0;
@@ -73,8 +82,23 @@ __host__ __device__ __forceinline__ bool fta_seg_empty(const FtaSeg& s) { return
 
 struct FtaBalanced {
   const int* pre;  // [B+1]
-  int B, U, n_tree, per, pad;
+  int B, U, n_tree, per, pad, lanes;  // U: entries per sequence on the line
   long long total;
+
+  __host__ __device__ void init(const int* pre_, int B_, const FtaGeom& g, int grid) {
+    pre = pre_; B = B_; n_tree = g.n_tree; pad = g.pad;
+    lanes = g.lanes > 0 ? g.lanes : 1;
+    U = g.U / lanes;
+    total = (long long)U * pre[B];
+    per = choose_per(total, grid / lanes > 0 ? grid / lanes : 1, g.min_per);
+  }
+  // line range [lin, end) of block c of `grid`; false if it has none
+  __host__ __device__ bool range(int c, int grid, long long& lin, long long& end) const {
+    if (c >= (grid / lanes) * lanes) return false;  // blocks left over after the last whole group
+    lin = (long long)(c / lanes) * per;
+    end = lin + per < total ? lin + per : total;
+    return lin < end;
+  }
 
   __host__ __device__ static int choose_per(long long total, int grid, int min_per) {
     long long per = (total + grid - 1) / (grid > 0 ? grid : 1);
@@ -97,7 +121,8 @@ struct FtaBalanced {
   // line position where the piece ends.  I is the integer type of line positions: 32-bit
   // arithmetic when the whole line fits (64-bit division is slow on the device).
   template <typename I>
-  __host__ __device__ long long segment_at_t(int c, I lin, FtaSeg& s) const {
+  __host__ __device__ long long segment_at_t(int cphys, I lin, FtaSeg& s) const {
+    const int c = cphys / lanes, lane = cphys - c * lanes;  // group of blocks, M tile within the KV head
     const I cbeg = (I)c * (I)per;
     I cend = cbeg + (I)per;
     if (cend > (I)total) cend = (I)total;
@@ -115,7 +140,7 @@ struct FtaBalanced {
     t1 = t1 < nreal ? t1 : nreal;
     const int cfirst = (int)(ustart / (I)per), clast = (int)((ustart + (I)(nreal - 1)) / (I)per);
     s.b = b;
-    s.j = j;
+    s.j = j * lanes + lane;
     s.c0 = (r0 < nb ? r0 : nb) * FTA_TILE;
     s.c1 = (t1 < nb ? t1 : nb) * FTA_TILE;  // caller clamps to L_b
     s.tt0 = (r0 > nb ? r0 : nb) - nb;
@@ -123,8 +148,8 @@ struct FtaBalanced {
     if (s.tt1 < s.tt0) s.tt1 = s.tt0;
     s.split = c - cfirst;
     s.nsplit = clast - cfirst + 1;
-    s.slot = 2 * c + (lin == cbeg ? 0 : 1);
-    s.p0slot = 2 * cfirst + (ustart == (I)cfirst * (I)per ? 0 : 1);
+    s.slot = 2 * cphys + (lin == cbeg ? 0 : 1);
+    s.p0slot = 2 * (cfirst * lanes + lane) + (ustart == (I)cfirst * (I)per ? 0 : 1);
     return (long long)send;
   }
   __host__ __device__ long long segment_at(int c, long long lin, FtaSeg& s) const {
@@ -187,7 +212,7 @@ __host__ __device__ __forceinline__ bool fta_row(const FtaParams& p, const FtaGe
 
 // BALANCED workspace: partial O rows [2*grid][R][D] fp32, partial LSEs [2*grid][R] fp32, then one
 // int4 per stage-1 block: the unit whose SECOND piece opens that block, {b, j, pieces, slot of the
-// first piece}, or pieces = 0.  Pieces after the first sit in slot 2*(block of the second piece + i - 1).
+// first piece}, or pieces = 0.  Piece i >= 1 sits in slot 2*(block of the second piece + (i - 1)*lanes).
 // Stage 2 launches one group of blocks per stage-1 block and merges exactly the units that were cut.
 __device__ __forceinline__ int4* fta_cut_desc(const FtaParams& p, const FtaGeom& g) {
   float* ws_o = reinterpret_cast<float*>(p.workspace);

@@ -119,11 +119,8 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
   if (p.split_mode == FTA_SPLIT_BALANCED) {
     fta_build_prefix(p, g.n_tree, g.pad, pre);
     __syncthreads();
-    plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree; plan.pad = g.pad;
-    plan.total = (long long)g.U * pre[p.B];
-    plan.per = FtaBalanced::choose_per(plan.total, gridDim.x, g.min_per);
-    lin = (long long)blockIdx.x * plan.per;
-    lin_end = lin + plan.per < plan.total ? lin + plan.per : plan.total;
+    plan.init(pre, p.B, g, gridDim.x);
+    if (!plan.range(blockIdx.x, gridDim.x, lin, lin_end)) lin = lin_end = 0;
     if (tid == 0) fta_cut_desc(p, g)[blockIdx.x] = make_int4(0, 0, 0, 0);  // rewritten below if a cut unit opens this block
   } else {
     item = blockIdx.x;

@@ -101,11 +101,8 @@ struct Walker {
   __device__ Walker(const FtaParams& p_, const FtaGeom& g_, const int* pre) : p(p_), g(g_) {
     lin = lin_end = item = n_items = 0;
     if (p.split_mode == FTA_SPLIT_BALANCED) {
-      plan.pre = pre; plan.B = p.B; plan.U = g.U; plan.n_tree = g.n_tree; plan.pad = g.pad;
-      plan.total = (long long)g.U * pre[p.B];
-      plan.per = FtaBalanced::choose_per(plan.total, gridDim.x, g.min_per);
-      lin = (long long)blockIdx.x * plan.per;
-      lin_end = lin + plan.per < plan.total ? lin + plan.per : plan.total;
+      plan.init(pre, p.B, g, gridDim.x);
+      if (!plan.range(blockIdx.x, gridDim.x, lin, lin_end)) lin = lin_end = 0;
     } else {
       item = blockIdx.x;
       n_items = (long long)p.B * g.U * (g.fixed_max_splits + 1);

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
           const int s = s0 + k;
           lse[k] = -INFINITY; o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (s < np) {
-            const long long slot = s == 0 ? (long long)cut.w : 2ll * ((long long)blockIdx.x + s - 1);
+            const long long slot = s == 0 ? (long long)cut.w : 2ll * ((long long)blockIdx.x + (long long)(s - 1) * g.lanes);
             lse[k] = ws_l[slot * g.R + row];
             o[k] = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row) * D + c4);
           }
