@@ -69,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -77,7 +77,6 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -347,6 +346,13 @@ def main():
     m1.record()
     torch.cuda.synchronize()
     ms_stage2 = m0.elapsed_time(m1) / args.steps
+    # The timed regions last milliseconds, nvidia-smi samples every 50 ms: keep the same call running
+    # (untimed) for half a second so that the clock record is one of this load, not of an idle GPU.
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 0.5:
+        for _ in range(50):
+            prep.run()
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public call, per-step inputs from pinned host memory ------
