@@ -234,6 +234,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (tid == 0) FTA_TRACE_EP(12, 0);
 
   if (warp < 4) {
     reg_dec<kRegsIssue>();
@@ -264,6 +265,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
           for (int i = 0; i < 4; ++i) dst[i] = src[i];
           mbar_arrive(BAR(B_SEGFULL + slot));  // release: the descriptor is visible to whoever sees the phase
+          if (k == 0) FTA_TRACE_EP(12, 1);
           if (!have) break;
         }
       }
@@ -281,15 +283,18 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           seg_copy(seg, &segq[sidx % kSegRing]);
           if (!seg.valid) break;
           const int n_ct = seg_cache_tiles(seg), n = n_ct + seg.tt1 - seg.tt0;
-          const int q_at = n < 2 ? n : 2;
+          const int q_at = sidx == 0 ? 0 : (n < 2 ? n : 2);  // nothing to overlap before the first piece: its Q goes first
+          if (sidx == 0) FTA_TRACE_EP(12, 2);
           // K tiles run two ahead of V tiles, as their consumers (S = Q K^T, O += P V) do.  The
           // first K tiles of a piece are requested before its Q tile: they do not depend on the
-          // Q buffer having been handed back, so they overlap the previous piece's tail.
+          // Q buffer having been handed back, so they overlap the previous piece's tail.  (The
+          // block's first piece has no predecessor and the first S waits for Q: there Q leads.)
           for (int u = 0; u < n + 2 && ok; ++u) {
             if (u == q_at) {
               ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
               if (!ok) break;
               mbar_expect_tx(BAR(B_QFULL), 2u * CS * (uint32_t)(g.qpt * g.hpt) * 128u);
+              if (sidx == 0) FTA_TRACE_EP(12, 3);
               const int h0 = seg.kvh * G + seg.gt * g.hpt, q0 = seg.qt * g.qpt;
 #pragma unroll
               for (int dup = 0; dup < CS; ++dup) {  // CS = 2: the same rows again at tile rows 64..
@@ -336,6 +341,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         if (!seg.valid) break;
         const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
         ok = wait_all(BAR(B_QREADY), sidx & 1, abort_flag, 0x201);  // Q rows are in TMEM
+        if (lane == 0 && sidx == 0) FTA_TRACE_EP(12, 6);
         if (lane == 0 && sidx > 0) FTA_TRACE_EP(sidx - 1, 5);
         for (int i = 0; i < n && ok; ++i) {
           const uint32_t t = gt + i, st = t % NS, sbuf = t % kNBuf;
@@ -444,6 +450,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     // Every S = Q K^T of the previous piece is complete when this runs (its last S has been read).
     auto q_to_tmem = [&](uint32_t piece) -> bool {
       if (!wait_all(BAR(B_QFULL), piece & 1, abort_flag, 0x306)) return false;
+      if (row == 0 && piece == 0) FTA_TRACE_EP(12, 4);
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t qr[32];
@@ -457,6 +464,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(BAR(B_QREADY));
+      if (row == 0 && piece == 0) FTA_TRACE_EP(12, 5);
       return true;
     };
     // V rows past the end of the sequence are zeroed so that 0 * padding cannot give NaN
