@@ -236,7 +236,9 @@ def workload_config(w, lens):
         "workload": f"{w.name}: B={w.B} H={w.H} kv_group_num={w.G} D={w.D} q_len={w.Q} "
                     f"{str(w.dtype).split('.')[-1]} ctx={w.ctx} lens={w.lens} tree={w.tree} block_size={w.block_size}",
         "sum_kv_len": int(sum(lens)),
-        "l2": "inputs larger than L2: the KV rows one call streams exceed the 126 MB L2, no flush needed",
+        "l2": ("inputs larger than L2: the KV rows one call streams exceed the 126 MB L2, no flush needed"
+               if 2 * 2 * w.D * (w.H // w.G) * sum(lens) > (126 << 20) else
+               "inputs smaller than L2 and not flushed between iterations: a launch-latency figure, not a bandwidth one"),
     }
 
 
