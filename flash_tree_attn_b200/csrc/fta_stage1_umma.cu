@@ -61,15 +61,22 @@ constexpr uint32_t OFF_RING = OFF_Q + kQBytes;
 constexpr uint32_t kBarBytes = 512;
 constexpr int kSegRing = 8;                  // pieces of work the planner may run ahead
 constexpr uint32_t kSegBytes = kSegRing * 64;
-// TMEM columns (32-bit): O fp32 | S fp32 x3 | Q 16-bit pairs | P 16-bit pairs x3.  Three S and P
-// buffers let S = Q K^T run three tiles ahead of the softmax and take PV(t-3), not PV(t-2), as the
-// product a new P must not overwrite: neither wait is then ever on the softmax's critical path.
+// TMEM columns (32-bit).  Several S buffers let S = Q K^T run ahead of the softmax; a P buffer is
+// not overwritten before the product that read it, PV(t - buffers), is complete, and S(t) is not
+// issued before that either, so neither wait is on the softmax's path.
+//   three buffers:  O fp32 0..127 | S fp32 128 + 64 k (k < 3) | Q 16-bit pairs 320..383 | P 16-bit
+//                   pairs 384 + 32 k | row statistics 480..481.
+//   four buffers (template PAIRS, where the softmax takes full tiles two at a time):  O 0..127 |
+//                   S/P 128 + 64 k (k < 4): a thread has all of its S row in registers before it
+//                   writes P, so P(t) goes over the first 32 columns of S(t) | Q 384..447 | row
+//                   statistics 448..449.
 constexpr uint32_t kTmemCols = 512;
-constexpr int kNBuf = 3;
+constexpr int kMaxBuf = 4;
+__host__ __device__ constexpr int n_buf(bool pairs) { return pairs ? 4 : 3; }
 constexpr uint32_t kColS = 128;  // + 64 * buffer
-constexpr uint32_t kColQ = 320;  // 64 columns: 128 head-dim elements, two per column
-constexpr uint32_t kColP = 384;  // + 32 * buffer: 64 KV columns, two per column
-constexpr uint32_t kColStat = 480;  // a row's running maximum and sum, handed from the softmax to the epilogue warps
+__host__ __device__ constexpr uint32_t col_q(bool pairs) { return pairs ? 384u : 320u; }  // 64 columns: 128 head-dim elements, two per column
+__host__ __device__ constexpr uint32_t col_p(bool pairs, uint32_t buf) { return pairs ? kColS + 64u * buf : 384u + 32u * buf; }
+__host__ __device__ constexpr uint32_t col_stat(bool pairs) { return pairs ? 448u : 480u; }
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
 constexpr uint32_t kXBytes = 2 * 64 * 64 * 4 + 2 * 64 * 2 * 4;  // CS = 2: per half 64 rows x 64 unnormalised O columns, and (m, l) per row
 constexpr size_t smem_bytes(int ns, int B, int cs) {
@@ -79,8 +86,8 @@ constexpr size_t smem_bytes(int ns, int B, int cs) {
 // mbarrier slots (ring barriers are sized for the largest ring)
 constexpr int kMaxNS = 6;
 enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
-       B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + 3,
-       B_FINAL = B_PREADY + 3, B_XFULL = B_FINAL + 2, B_XFREE, B_SEGFULL, B_SEGFREE = B_SEGFULL + kSegRing,
+       B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + kMaxBuf,
+       B_FINAL = B_PREADY + kMaxBuf, B_XFULL = B_FINAL + 2, B_XFREE, B_SEGFULL, B_SEGFREE = B_SEGFULL + kSegRing,
        B_STATS = B_SEGFREE + kSegRing, B_STATSFREE, B_COUNT };
 // A parity wait is only meaningful while the barrier is at most one phase ahead of the phase
 // asked for.  PV(t) therefore commits to B_ODONE + (t & 3): whoever has seen S(t') ready knows
@@ -170,12 +177,15 @@ __device__ __forceinline__ void seg_copy(SegDesc& d, const SegDesc* src) {
   for (int i = 0; i < 4; ++i) d4[i] = s4[i];
 }
 
-template <typename T, int NS, int CS>
+template <typename T, int NS, int CS, bool PAIRS>
 __global__ void __launch_bounds__(kThreads, 1)
 stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ Maps maps) {
   constexpr uint32_t OFF_X = OFF_RING + NS * kStage;
   constexpr uint32_t OFF_BAR = OFF_X + (CS == 2 ? kXBytes : 0);
   constexpr uint32_t OFF_SEG = OFF_BAR + kBarBytes;
+  static_assert(!(PAIRS && CS == 2), "tiles are taken in pairs only without the column split");
+  constexpr int kNBuf = n_buf(PAIRS);
+  constexpr uint32_t kColQ = col_q(PAIRS), kColStat = col_stat(PAIRS);
   constexpr uint32_t OFF_PRE = OFF_SEG + kSegBytes;
   // Swizzle atoms are 1024-byte aligned.  Without the column split there is room to round the base
   // up; with it every kilobyte is taken, the declared alignment is relied on and checked.
@@ -408,7 +418,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
             const uint64_t dV = dV0 + (uint64_t)((st * kStage) >> 4);
 #pragma unroll
             for (int kk = 0; kk < FTA_TILE / 16; ++kk)
-              umma_f16_ts(tmem, tmem + kColP + 32 * sbuf + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
+              umma_f16_ts(tmem, tmem + col_p(PAIRS, sbuf) + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
                           (i > 0 || kk > 0) ? 1u : 0u);
             umma_commit(BAR(B_VEMPTY + st));
             umma_commit(BAR(B_ODONE + (t & 3)));
@@ -438,7 +448,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
       for (int k = 0; k < 16; ++k) z[k] = 0u;
 #pragma unroll
-      for (int k = 0; k < kNBuf; ++k) tmem_st16(t_lane + kColP + 32 * k + 16 * (chalf ^ 1), z);
+      for (int k = 0; k < kNBuf; ++k) tmem_st16(t_lane + col_p(PAIRS, k) + 16 * (chalf ^ 1), z);
       tmem_st_wait();
       tc_fence_before();
     }
@@ -519,6 +529,86 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       } else {
         for (int i = 0; i < n; ++i) {
           const uint32_t t = gt + i, sbuf = t % kNBuf;
+          if (PAIRS && scale2 > 0.f && i + 1 < n_ct && seg.c1 - (seg.c0 + (i + 1) * FTA_TILE) >= FTA_TILE) {
+            // ---- two full cache tiles at once ------------------------------------------------
+            // Everything that costs a round trip (barrier wait, TMEM load, the vote on the running
+            // maximum, TMEM store, hand-off) is paid once for 128 KV rows.  The four S/P buffers let
+            // the next two products be computed meanwhile.
+            const uint32_t t1 = t + 1, sb1 = t1 % kNBuf;
+            ok = wait_all(BAR(B_SFULL + sbuf), (t / kNBuf) & 1, abort_flag, 0x301);
+            if (!ok) break;
+            ok = wait_all(BAR(B_SFULL + sb1), (t1 / kNBuf) & 1, abort_flag, 0x301);
+            if (!ok) break;
+            if (row == 0) { FTA_TRACE(t, 3); FTA_TRACE(t1, 3); }
+            tc_fence_after();
+            float sa[64], sb[64];
+            tmem_ld32(t_lane + kColS + FTA_TILE * sbuf, sa);
+            tmem_ld32(t_lane + kColS + FTA_TILE * sbuf + 32, sa + 32);
+            tmem_ld32(t_lane + kColS + FTA_TILE * sb1, sb);
+            tmem_ld32(t_lane + kColS + FTA_TILE * sb1 + 32, sb + 32);
+            tmem_ld_wait();
+            float mx[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) mx[c] = fmax3(sa[c], sa[c + 8], sa[c + 16]);
+#pragma unroll
+            for (int c = 24; c + 8 < 64; c += 16)
+#pragma unroll
+              for (int k = 0; k < 8; ++k) mx[k] = fmax3(mx[k], sa[c + k], sa[c + 8 + k]);
+#pragma unroll
+            for (int c = 0; c < 64; c += 16)
+#pragma unroll
+              for (int k = 0; k < 8; ++k) mx[k] = fmax3(mx[k], sb[c + k], sb[c + 8 + k]);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], sa[56 + c]);
+            const float mt = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]))) * scale2;
+            const bool need = mt > m_used + 8.f;
+            if (i > 0 && __any_sync(0xffffffffu, need)) {
+              ok = wait_all(BAR(B_ODONE + ((t - 1) & 3)), ((t - 1) >> 2) & 1, abort_flag, 0x302);
+              if (!ok) break;
+              tc_fence_after();
+              const float alpha = need ? fta_exp2(m_used - mt) : 1.f;
+#pragma unroll
+              for (int ch = 0; ch < kD / 32; ++ch) {
+                float o[32];
+                tmem_ld32(t_lane + ch * 32, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int k = 0; k < 32; ++k) o[k] *= alpha;
+                tmem_st32(t_lane + ch * 32, o);
+              }
+              tmem_st_wait();
+            }
+            if (need) {
+              l *= fta_exp2(m_used - mt);
+              m_used = mt;
+            }
+            const float nsub = m_used == -INFINITY ? 0.f : -m_used;
+            float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const float* sv = half == 0 ? sa : sb;
+              uint32_t pk[32];
+#pragma unroll
+              for (int c2 = 0; c2 < 32; ++c2) {
+                const float2 e = ffma2(make_float2(sv[2 * c2], sv[2 * c2 + 1]), make_float2(scale2, scale2), make_float2(nsub, nsub));
+                float p0, p1;
+                if (c2 & 1) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
+                else { p0 = fta_exp2(e.x); p1 = fta_exp2(e.y); }
+                ps[c2 & 3] += p0 + p1;
+                pk[c2] = FtaType<T>::pack(p0, p1);
+              }
+              const uint32_t sbh = half == 0 ? sbuf : sb1;
+              if (row == 0) FTA_TRACE(half == 0 ? t : t1, 4);
+              tmem_st32(t_lane + col_p(PAIRS, sbh), reinterpret_cast<const float*>(pk));  // over the S columns just read
+              tmem_st_wait();
+              tc_fence_before();
+              mbar_arrive(BAR(B_PREADY + sbh));
+              if (row == 0) FTA_TRACE(half == 0 ? t : t1, 5);
+            }
+            l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+            ++i;  // the loop's own increment takes the second tile
+            continue;
+          }
           const bool is_tree = i >= n_ct;
           int valid, col0 = 0;
           if (!is_tree) {
@@ -638,8 +728,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
           // P[t%3] was the A operand of PV(t-3), which completed before S(t) was even issued
           if (row == 0) FTA_TRACE(t, 4);
-          if (CS == 2) tmem_st16(t_lane + kColP + 32 * sbuf + 16 * chalf, pk);
-          else tmem_st32(t_lane + kColP + 32 * sbuf, reinterpret_cast<const float*>(pk));
+          if (CS == 2) tmem_st16(t_lane + col_p(PAIRS, sbuf) + 16 * chalf, pk);
+          else tmem_st32(t_lane + col_p(PAIRS, sbuf), reinterpret_cast<const float*>(pk));  // over the S columns just read
           if (!is_tree && valid < FTA_TILE) {
             ok = zero_v_tail(t, valid);
             if (!ok) break;
@@ -1159,18 +1249,26 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   void (*kern)(const FtaParams, const FtaGeom, const Maps);
   const bool f16 = p.dtype == FTA_DTYPE_F16;
+  // Tiles are taken two at a time (and a fourth S/P buffer is used) only where the blocks are fed
+  // through L2: several M tiles per KV head walking the same tiles (lanes).  Where every block streams
+  // its own K/V from DRAM, letting the products and the softmax run further ahead makes the blocks
+  // compete for memory unevenly and the slowest one ends later (measured on cfg 3: +8 %).
+  const bool pairs = cs == 1 && g.lanes > 1;
   if (cs == 2) {
-    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 2> : stage1_umma_kernel<__half, 5, 2>;
-    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 2> : stage1_umma_kernel<__nv_bfloat16, 5, 2>;
+    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 2, false> : stage1_umma_kernel<__half, 5, 2, false>;
+    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 2, false> : stage1_umma_kernel<__nv_bfloat16, 5, 2, false>;
+  } else if (pairs) {
+    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 1, true> : stage1_umma_kernel<__half, 5, 1, true>;
+    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 1, true> : stage1_umma_kernel<__nv_bfloat16, 5, 1, true>;
   } else {
-    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 1> : stage1_umma_kernel<__half, 5, 1>;
-    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 1> : stage1_umma_kernel<__nv_bfloat16, 5, 1>;
+    if (f16) kern = ns == 6 ? stage1_umma_kernel<__half, 6, 1, false> : stage1_umma_kernel<__half, 5, 1, false>;
+    else kern = ns == 6 ? stage1_umma_kernel<__nv_bfloat16, 6, 1, false> : stage1_umma_kernel<__nv_bfloat16, 5, 1, false>;
   }
-  static unsigned long long configured[8] = {0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull};
+  static unsigned long long configured[12] = {0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull, 0ull};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  const int ti = (f16 ? 0 : 1) + (ns == 6 ? 0 : 2) + (cs == 2 ? 4 : 0);
+  const int ti = (f16 ? 0 : 1) + (ns == 6 ? 0 : 2) + (cs == 2 ? 4 : (pairs ? 8 : 0));
   if (!((configured[ti] >> (dev & 63)) & 1ull)) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
