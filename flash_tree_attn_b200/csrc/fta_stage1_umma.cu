@@ -25,6 +25,10 @@
 // Registers are rebalanced with setmaxnreg (64 per thread for warps 0..3, 240 for the softmax, 200
 // for the epilogue).
 //
+// Tile pairs (template PAIRS, no column split): the softmax takes full cache tiles two at a time, so
+// that everything that costs a round trip is paid once per 128 KV rows; four S buffers, P written
+// over the S columns just read.  Chosen by the launcher where blocks are fed through L2.
+//
 // Column split (template CS = 2): when a unit has at most 64 query rows (q_len 64 without GQA),
 // rows 64..127 of the tile repeat rows 0..63 (Q is loaded twice) and each half of the tile's rows
 // works on its own 32 of every tile's 64 KV columns, with its own running max, row sum and O rows.
