@@ -201,7 +201,7 @@ __device__ __forceinline__ void tmem_ld2(uint32_t taddr, float& a, float& b) {
   b = __uint_as_float(y);
 }
 
-// Register budget of the calling warpgroup (four consecutive warps, all of which must execute it):
+// Register allowance of the calling warpgroup (four consecutive warps, all of which must execute it):
 // warps that only wait and issue give registers back, the softmax warps take them.
 template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }

@@ -2,7 +2,7 @@
 (flash_tree_attn.py:216-376) on seeded inputs, on CPU, under the Triton interpreter.
 
 Run in the development container only (it needs the reference checkout):
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py [/path/to/reference]
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference
 The reference module cannot be imported as is: it runs a CUDA benchmark at import
 (flash_tree_attn.py:487).  Lines 1-376 plus its late `import torch.nn.functional as F`
 (:401) are loaded from a temporary copy outside this repository (triton.jit needs a real
@@ -50,7 +50,9 @@ CASES = {
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <directory holding the reference's flash_tree_attn.py>")
+    ref = load_reference(sys.argv[1])
     torch.manual_seed(0)
     for name, (w, allowed) in CASES.items():
         inp = make_inputs(w, "cpu", allowed=allowed)

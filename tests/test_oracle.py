@@ -13,7 +13,7 @@ def test_fp32_oracle_matches_reference_output(name):
     g = load_golden(name)
     o = tree_attention_oracle(g["q"], g["k_cache"], g["v_cache"], g["current_k"], g["current_v"], g["mask"],
                               g["kv_seq_len"], None, g["kv_group_num"])
-    # the reference computes in fp16 with 16-bit LSEs: the budget of its own test is 1e-2
+    # the reference computes in fp16 with 16-bit LSEs: the tolerance of its own test is 1e-2
     # (flash_tree_attn.py:440); observed agreement is far tighter
     err = (o["out"] - g["ref_out"].float()).abs().max().item()
     assert err < 2e-3, err
