@@ -764,7 +764,12 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if (seg.valid) ok = q_to_tmem(sidx);
       if (row == 0) FTA_TRACE_EP(sidx - 1, 2);
     }
-    if (row == 0) { FTA_BLK(1, clock64() - prof_t0); FTA_BLK(3, (long long)sidx); }
+    if (row == 0) {
+      unsigned int smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      FTA_BLK(1, clock64() - prof_t0);
+      FTA_BLK(3, (long long)sidx + 1000ll * smid + 1000000ll * gt);  // pieces, SM, tiles
+    }
   } else {
     // ================================ epilogue =======================================
     // O row / l and the LSE of every piece, while the softmax warps are already at work on the
