@@ -176,8 +176,12 @@ def seq_split_arm(args, w, fta, dev, rank, world, dist):
     k_sh, v_sh = inp["k_cache"][:, :, lo:hi], inp["v_cache"][:, :, lo:hi]
     shard_len = torch.tensor([max(0, min(lens[0], hi) - lo)], dtype=torch.int32, device=dev)
 
+    xch = None
+    if args.exchange == "peer":
+        xch = fdist.PeerExchange(w.B * w.H * w.Q * w.D, w.B * w.H * w.Q, dev)
+
     def step(q, ck, cv, mask):
-        return fdist.kv_range_decode(q, k_sh, v_sh, ck, cv, mask, shard_len, w.block_size, w.G)
+        return fdist.kv_range_decode(q, k_sh, v_sh, ck, cv, mask, shard_len, w.block_size, w.G, exchange=xch)
 
     def sync():
         torch.cuda.synchronize()
@@ -215,6 +219,8 @@ def seq_split_arm(args, w, fta, dev, rank, world, dist):
     x1.record()
     sync()
     ms_e2e = x0.elapsed_time(x1)
+    if xch is not None:
+        xch.check()  # raises if a wait for a peer ever ran out
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(t[0]), float(t[1])
@@ -227,11 +233,13 @@ def seq_split_arm(args, w, fta, dev, rank, world, dist):
             "metric": "tree_attn_calls_per_s", "value": calls_s, "unit": "calls/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload_config(w, lens), parallelism=f"kv-range x{world}, one all-gather + merge per call"),
+            "config": dict(workload_config(w, lens), parallelism=f"kv-range x{world}, " + (
+                "one exchange-merge kernel per call over peer-mapped memory" if xch is not None
+                else "one all-gather + merge per call")),
             "kv_read_gbs": kvb * calls_s / 1e9, "tflops": tfl,
             "roofline": {"bound": "tensor", "achieved": tfl, "peak": tf_peak * world, "unit": "TFLOP/s",
                          "frac": tfl / (tf_peak * world), "traffic": None, "peak_source": peak_src,
-                         "kernel": "whole call (stage 1 + all-gather + merge)"},
+                         "kernel": "whole call (stage 1 + stage 2 + " + ("exchange-merge)" if xch is not None else "all-gather + merge)")},
             "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "calls/s",
                     "h2d_bytes_per_step": sum(host[n].numel() * host[n].element_size() for n in names),
                     "d2h_bytes_per_step": out_host.numel() * out_host.element_size(),
@@ -239,6 +247,8 @@ def seq_split_arm(args, w, fta, dev, rank, world, dist):
                             "KV cache shards resident in HBM"},
             "gpu_launches": 3 * args.steps, "clocks": clocks,
         }))
+    if xch is not None:
+        xch.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -268,6 +278,9 @@ def main():
     ap.add_argument("--paged", type=int, default=0, metavar="PAGE_SIZE",
                     help="house the KV cache in shuffled pages of this many rows (multiple of 64) and "
                          "run the device-timed region through the block table (implies --skip-e2e)")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="sequence-split arm (one long sequence on several GPUs): 'peer' = one exchange-merge "
+                         "kernel per rank over peer-mapped memory, 'nccl' = all-gather + merge kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -81,6 +81,20 @@ class FtaCommitParams(C.Structure):
     ]
 
 
+FTA_MAX_RANKS = 8
+
+
+class FtaExchangeParams(C.Structure):
+    """Mirror of `struct FtaExchangeParams` (include/fta.h)."""
+
+    _fields_ = [
+        ("part", _vp * FTA_MAX_RANKS), ("flag_peer", _vp * FTA_MAX_RANKS),
+        ("flag_local", _vp), ("status", _vp), ("timeout_ns", _i64),
+        ("world", _i32), ("rank", _i32), ("epoch", C.c_uint32), ("rows", _i32), ("D", _i32), ("out_dtype", _i32),
+        ("out", _vp), ("lse", _vp),
+    ]
+
+
 # every symbol include/fta.h declares: (restype, argtypes)
 SYMBOLS = {
     "fta_version": (C.c_int, []),
@@ -94,6 +108,7 @@ SYMBOLS = {
     "fta_stage2": (C.c_int, [C.POINTER(FtaParams), _vp]),
     "fta_merge_parts": (C.c_int, [C.POINTER(FtaMergeParams), _vp]),
     "fta_commit_accepted": (C.c_int, [C.POINTER(FtaCommitParams), _vp]),
+    "fta_exchange_merge": (C.c_int, [C.POINTER(FtaExchangeParams), _vp]),
     "fta_plan_host": (_i64, [C.POINTER(FtaParams), C.POINTER(_i64), C.POINTER(_i64), _i64,
                              C.POINTER(_i32), C.POINTER(_i32)]),
     "fta_plan_grid": (C.c_int, [C.POINTER(FtaParams)]),

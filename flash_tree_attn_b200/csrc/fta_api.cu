@@ -18,6 +18,7 @@ int fta_umma_supported(const FtaParams&);
 cudaError_t fta_launch_stage2(const FtaParams&, const FtaGeom&, cudaStream_t);
 cudaError_t fta_launch_commit(const FtaCommitParams&, cudaStream_t);
 cudaError_t fta_launch_merge_parts(const FtaMergeParams&, cudaStream_t);
+cudaError_t fta_launch_exchange_merge(const FtaExchangeParams&, cudaStream_t);
 
 // Scratch of fta_decode_static: partial results of the BALANCED plan live here instead of in a
 // caller-provided workspace.  The array is part of the library image: every GPU that loads the
@@ -293,6 +294,20 @@ int fta_merge_parts(const FtaMergeParams* p, void* stream) {
   if (p->out_dtype < FTA_DTYPE_F16 || p->out_dtype > FTA_DTYPE_F32) return FTA_E_BADARG;
   if (p->rows == 0) return FTA_OK;
   cudaError_t e = fta_launch_merge_parts(*p, (cudaStream_t)stream);
+  return e == cudaSuccess ? FTA_OK : cuda_fail(e);
+}
+
+int fta_exchange_merge(const FtaExchangeParams* p, void* stream) {
+  if (!p || !p->out || !p->flag_local || !p->status) return FTA_E_BADARG;
+  if (p->world < 1 || p->world > FTA_MAX_RANKS || p->rank < 0 || p->rank >= p->world) return FTA_E_BADARG;
+  if (p->rows < 0 || p->D < 4 || p->D % 4 != 0 || p->timeout_ns <= 0) return FTA_E_BADARG;
+  if (p->out_dtype < FTA_DTYPE_F16 || p->out_dtype > FTA_DTYPE_F32 || !aligned(p->out, 16)) return FTA_E_BADARG;
+  for (int s = 0; s < p->world; ++s) {
+    if (!p->part[s] || !aligned(p->part[s], 16)) return FTA_E_BADARG;
+    if (s != p->rank && (!p->flag_peer[s] || !aligned(p->flag_peer[s], 4))) return FTA_E_BADARG;
+  }
+  if (p->rows == 0) return FTA_OK;
+  cudaError_t e = fta_launch_exchange_merge(*p, (cudaStream_t)stream);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 

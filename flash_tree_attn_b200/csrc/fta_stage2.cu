@@ -142,7 +142,91 @@ __global__ void __launch_bounds__(kThreads) merge_parts_kernel(const FtaMergePar
   }
 }
 
+// ---- exchange + merge for KV-range shards on several GPUs ------------------------------------
+// Every rank keeps its packed partial ([rows, D] O then [rows] LSE, fp32) in memory its peers have
+// mapped.  One launch per rank: block 0 tells every peer "my partial of call `epoch` is complete"
+// with a release store into the peer's flag array, every block waits until each peer has said the
+// same (acquire loads of this rank's own flag array, bounded by a timeout), then the merge reads
+// the peers' partials with plain loads over NVLink and folds them in rank order.
+//   * The partial was written by earlier kernels on this stream, so it is complete when this kernel
+//     starts; the peers read it where it lives (pull), so no data has to be ordered after a flag.
+//   * Flags only grow (the epoch of the last finished call), so nothing is ever reset.
+//   * A rank rewrites a buffer two calls later.  A peer that still reads the buffer of call e has
+//     not yet signalled e + 1, and this rank's call e + 1 waits for that signal before it ends, so
+//     two alternating buffers are enough.
+//   * When a wait runs out the block leaves without storing and sets *status; the host reads it.
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads) exchange_merge_kernel(const FtaExchangeParams p) {
+  __shared__ int s_fail;
+  const int t = threadIdx.x;
+  if (t == 0) s_fail = 0;
+  __syncthreads();
+  if (t < p.world && t != p.rank) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(p.flag_peer[t], p.epoch);
+    }
+    const unsigned long long t0 = global_ns();
+    unsigned spins = 0;
+    while ((int)(ld_acquire_sys(p.flag_local + t) - p.epoch) < 0) {
+      if ((++spins & 31u) == 0 && global_ns() - t0 > (unsigned long long)p.timeout_ns) {
+        atomicOr(&s_fail, 1 << t);
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+  if (s_fail) {
+    if (t == 0) atomicOr(p.status, s_fail);
+    return;
+  }
+  const int D4 = p.D >> 2;
+  const long long n = (long long)p.rows * D4;
+  const long long lse_off = (long long)p.rows * p.D;
+  for (long long i = (long long)blockIdx.x * kThreads + t; i < n; i += (long long)gridDim.x * kThreads) {
+    const long long row = i / D4;
+    const int c4 = (int)(i - row * D4) * 4;
+    float lse[FTA_MAX_RANKS];
+    float4 o[FTA_MAX_RANKS];
+#pragma unroll
+    for (int s = 0; s < FTA_MAX_RANKS; ++s)
+      if (s < p.world) {
+        lse[s] = __ldcg(p.part[s] + lse_off + row);
+        o[s] = __ldcg(reinterpret_cast<const float4*>(p.part[s] + row * p.D + c4));
+      }
+    Acc acc; acc.init();
+#pragma unroll
+    for (int s = 0; s < FTA_MAX_RANKS; ++s)
+      if (s < p.world) acc.add(lse[s], o[s]);
+    fta_store4(p.out, p.out_dtype, row * p.D + c4, acc.value());
+    if (c4 == 0 && p.lse) p.lse[row] = acc.lse();
+  }
+}
+
 }  // namespace
+
+cudaError_t fta_launch_exchange_merge(const FtaExchangeParams& p, cudaStream_t st) {
+  const long long n = (long long)p.rows * (p.D >> 2);
+  long long blocks = (n + kThreads - 1) / kThreads;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  exchange_merge_kernel<<<(int)blocks, kThreads, 0, st>>>(p);
+  return cudaGetLastError();
+}
 
 cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
   const bool balanced = p.split_mode == FTA_SPLIT_BALANCED;

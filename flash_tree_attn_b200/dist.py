@@ -8,12 +8,17 @@ independent, flash_tree_attn.py:49-51,71-73; the LSE merge is associative, :195-
   (O, LSE); the tree tokens are attached to the last rank's range; ONE all-gather of the
   packed partials, then the merge kernel on every rank (`kv_range_decode`).
 
+  `kv_range_decode(..., exchange=PeerExchange(...))` replaces the all-gather and the merge by ONE
+  kernel per rank that signals, waits (bounded) and reads the peers' partials over NVLink from
+  memory the ranks mapped into each other once (`fta_exchange_merge`).
+
 The packing, gather and merge are written against an injectable `decode_fn` / `merge_fn` so
 that the host logic runs on CPU ranks (gloo) in the tests; on GPUs the defaults are the CUDA
 operator and `fta_merge_parts`.
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
@@ -74,11 +79,107 @@ def _default_merge(po, pl, out_dtype):
     return merge_partials(po, pl, out_dtype)
 
 
+def exchange_layout(numel_o: int, numel_lse: int, world: int) -> Tuple[int, int, int]:
+    """Per-rank layout of the peer-mapped allocation, in 4-byte words: two packed partial
+    buffers (each [numel_o + numel_lse] fp32 rounded up to 16 bytes) then `world` uint32 flags.
+    Returns (buffer_stride, flags_offset, total)."""
+    stride = -(-(numel_o + numel_lse) // 4) * 4
+    flags = 2 * stride
+    return stride, flags, flags + -(-world // 4) * 4
+
+
+class PeerExchange:
+    """Peer-mapped partial buffers and flags of the ranks of one box, for `fta_exchange_merge`.
+
+    Construction is collective (every rank of `group`, same arguments).  The memory comes from
+    torch.distributed._symmetric_memory: one allocation per rank, mapped into every peer by its
+    rendezvous; only plain peer loads and stores are used on it.
+    The calls `mine()` ... `merge()` must come in the same order on every rank; the object counts
+    the epoch and alternates between the two buffers itself.
+    """
+
+    def __init__(self, numel_o: int, numel_lse: int, device: torch.device, group: Optional[dist.ProcessGroup] = None,
+                 timeout_s: float = 1.0):
+        from . import _lib
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > _lib.FTA_MAX_RANKS:
+            raise ValueError(f"at most {_lib.FTA_MAX_RANKS} ranks")
+        self.no, self.nl = int(numel_o), int(numel_lse)
+        self.stride, self.flags_off, total = exchange_layout(self.no, self.nl, self.world)
+        self.device = torch.device(device)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._keep = []
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        # plain peer mappings only: no NVLink multicast object is bound to this memory
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        self.local = symm_mem.empty(total, dtype=torch.float32, device=self.device)
+        self.local.zero_()
+        hdl = symm_mem.rendezvous(self.local, self.group)
+        self.base = [int(x) for x in hdl.buffer_ptrs]
+        self._keep.append(hdl)
+        assert self.base[self.rank] == self.local.data_ptr()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anyone signals
+
+    def mine(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(O, LSE) flat fp32 views of the buffer this rank fills for the NEXT merge()."""
+        off = ((self.epoch + 1) & 1) * self.stride
+        return self.local[off:off + self.no], self.local[off + self.no:off + self.no + self.nl]
+
+    def merge(self, o_shape, lse_shape, out_dtype: torch.dtype):
+        """Signal, wait for the peers, merge all ranks' partials: (out, lse) on this rank."""
+        from . import _lib
+        from .op import _DT
+
+        self.epoch += 1
+        D = int(o_shape[-1])
+        rows = self.nl
+        assert rows * D == self.no
+        out = torch.empty(tuple(o_shape), dtype=out_dtype, device=self.device)
+        lse = torch.empty(tuple(lse_shape), dtype=torch.float32, device=self.device)
+        p = _lib.FtaExchangeParams()
+        off = (self.epoch & 1) * self.stride * 4
+        for s in range(self.world):
+            p.part[s] = self.base[s] + off
+            p.flag_peer[s] = self.base[s] + (self.flags_off + self.rank) * 4
+        p.flag_local = self.base[self.rank] + self.flags_off * 4
+        p.status = self.status.data_ptr()
+        p.timeout_ns = self.timeout_ns
+        p.world, p.rank, p.epoch = self.world, self.rank, self.epoch & 0xFFFFFFFF
+        p.rows, p.D, p.out_dtype = rows, D, _DT[out_dtype]
+        p.out, p.lse = out.data_ptr(), lse.data_ptr()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.load().fta_exchange_merge(C.byref(p), stream), "fta_exchange_merge")
+        return out, lse
+
+    def check(self) -> None:
+        """Synchronise and raise if a wait for a peer ran out since the last check."""
+        st = int(self.status.item())
+        if st:
+            self.status.zero_()
+            late = [s for s in range(self.world) if st >> s & 1]
+            raise TimeoutError(f"rank {self.rank}: no signal from rank(s) {late} within {self.timeout_ns / 1e9:.1f} s")
+
+    def close(self) -> None:
+        """Collective: nobody unmaps while a peer may still read."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self._keep.clear()
+
+
 def kv_range_decode(
     q: torch.Tensor, k_shard: torch.Tensor, v_shard: torch.Tensor, current_k: torch.Tensor, current_v: torch.Tensor,
     mask: torch.Tensor, shard_len: torch.Tensor, block_size: int = 64, kv_group_num: int = 1,
     group: Optional[dist.ProcessGroup] = None, out_dtype: Optional[torch.dtype] = None,
     decode_fn: Callable = _default_decode, merge_fn: Callable = _default_merge,
+    exchange: Optional["PeerExchange"] = None,
 ):
     """Sequence-split decode.  Every rank passes the same q / current_k / current_v / mask and
     ITS OWN KV rows (`k_shard`, `v_shard`: [B, Hkv, rows_of_this_rank, D]; `shard_len` [B]: how
@@ -89,6 +190,13 @@ def kv_range_decode(
     rank = dist.get_rank(group)
     world = dist.get_world_size(group)
     B, H, Q, D = q.shape
+    if exchange is not None:
+        # the operator writes its partial into this rank's peer-mapped buffer; one kernel then
+        # signals, waits for the peers and merges what it reads from them
+        mo, ml = exchange.mine()
+        decode_fn(q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size, kv_group_num,
+                  rank == world - 1, out_buf=mo.view(B, H, Q, D), lse_buf=ml.view(B, H, Q))
+        return exchange.merge((B, H, Q, D), (B, H, Q), out_dtype or q.dtype)
     if decode_fn is _default_decode:
         # the operator writes its partial straight into this rank's slot of the packed buffer
         no, nl = B * H * Q * D, B * H * Q

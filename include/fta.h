@@ -155,6 +155,38 @@ typedef struct FtaMergeParams {
   float* lse;        /* optional [rows] */
 } FtaMergeParams;
 
+/*
+ * Exchange + merge of KV-range shard partials between the GPUs of one box, without a library
+ * collective: one launch per rank.  No counterpart in the reference (single GPU); the merge is
+ * flash_tree_attn.py:195-208 over one partial per rank, in rank order.
+ *   part[s]       rank s's packed partial as mapped in THIS process: rows*D floats of O, then
+ *                 rows floats of LSE; part[rank] is this rank's own.  Peer entries are device
+ *                 pointers of memory mapped from the peer (cuMemMap of an exported handle).
+ *   flag_peer[s]  address, as mapped here, of element [rank] of rank s's flag array
+ *   flag_local    this rank's flag array [world] (uint32, zero before the first call)
+ *   epoch         1, 2, 3, ... (mod 2^32) the same on every rank for the same call
+ *   status        device word; bit s is set when the wait for rank s ran out (nothing is stored)
+ *   timeout_ns    bound of that wait
+ * The caller alternates between two partial buffers from call to call (a peer may still read the
+ * previous one) and makes the calls in the same order on every rank.
+ */
+#define FTA_MAX_RANKS 8
+typedef struct FtaExchangeParams {
+  const float* part[FTA_MAX_RANKS];
+  uint32_t* flag_peer[FTA_MAX_RANKS];
+  const uint32_t* flag_local;
+  int32_t* status;
+  int64_t timeout_ns;
+  int32_t world;
+  int32_t rank;
+  uint32_t epoch;
+  int32_t rows;
+  int32_t D;
+  int32_t out_dtype; /* FTA_DTYPE_* */
+  void* out;         /* [rows, D] contiguous */
+  float* lse;        /* optional [rows] */
+} FtaExchangeParams;
+
 /* Library / ABI version (FTA_VERSION).  No counterpart in the reference. */
 int fta_version(void);
 
@@ -250,6 +282,9 @@ int fta_stage2(const FtaParams* p, void* stream);
 
 /* Merge of gathered shard partials (flash_tree_attn.py:195-208 on a fixed split count). */
 int fta_merge_parts(const FtaMergeParams* p, void* stream);
+
+/* Exchange + merge over peer-mapped memory (see FtaExchangeParams). */
+int fta_exchange_merge(const FtaExchangeParams* p, void* stream);
 
 /*
  * Host-side evaluation of the BALANCED plan, for tests and tooling: given lengths on

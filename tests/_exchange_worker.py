@@ -1,0 +1,78 @@
+"""Child process of the two-GPU exchange-merge test (one per GPU, started by torch.distributed.run).
+
+Every rank owns a contiguous KV range of one long sequence.  The same call goes through the NCCL
+path (all-gather of the packed partials, then fta_merge_parts) and through fta_exchange_merge over
+peer-mapped memory; both fold the ranks' partials in rank order with the same arithmetic, so the
+results must be identical bit for bit, many calls in a row (two alternating buffers, growing
+epochs).  Prints one line "EXCHANGE_OK ..." per rank on success.
+"""
+import os
+import sys
+
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    ctx = int(sys.argv[1]) if len(sys.argv) > 1 else 8192
+    iters = int(sys.argv[2]) if len(sys.argv) > 2 else 8
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from flash_tree_attn_b200 import dist as fdist
+    from flash_tree_attn_b200.workloads import Workload, make_inputs
+
+    w = Workload("xchg", 1, 64, 8, 128, 64, torch.bfloat16, ctx, "full", "random", seed=77)
+    inp = make_inputs(w, dev)  # same seed: every rank draws the same tensors
+    lo, hi = fdist.kv_ranges(ctx, world)[rank]
+    k_sh, v_sh = inp["k_cache"][:, :, lo:hi], inp["v_cache"][:, :, lo:hi]
+    shard_len = torch.tensor([hi - lo], dtype=torch.int32, device=dev)
+    B, H, Q, D = inp["q"].shape
+    xch = fdist.PeerExchange(B * H * Q * D, B * H * Q, dev, timeout_s=2.0)
+
+    def call(q, exchange):
+        return fdist.kv_range_decode(q, k_sh, v_sh, inp["current_k"], inp["current_v"], inp["mask"], shard_len,
+                                     w.block_size, w.G, exchange=exchange)
+
+    gen = torch.Generator(device=dev).manual_seed(5)
+    worst = 0.0
+    for _ in range(iters):
+        q = torch.randn(inp["q"].shape, generator=gen, device=dev, dtype=torch.float32).to(inp["q"].dtype)
+        o_ref, l_ref = call(q, None)
+        o_x, l_x = call(q, xch)
+        xch.check()
+        assert torch.equal(o_ref, o_x), f"rank {rank}: outputs differ, max {float((o_ref.float() - o_x.float()).abs().max())}"
+        assert torch.equal(l_ref, l_x), f"rank {rank}: LSEs differ"
+        worst = max(worst, float(o_x.float().abs().max()))
+    assert worst > 0.0 and torch.isfinite(o_x.float()).all()
+
+    def timed(exchange, n=30):
+        for _ in range(5):
+            call(inp["q"], exchange)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            call(inp["q"], exchange)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]) * 1e3
+
+    us_nccl, us_x = timed(None), timed(xch)
+    xch.check()
+    print(f"EXCHANGE_OK rank {rank}/{world} ctx {ctx}: all-gather+merge {us_nccl:.1f} us/call, "
+          f"exchange-merge {us_x:.1f} us/call", flush=True)
+    xch.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -37,6 +37,27 @@ def test_struct_layout_matches_header():
     # sizes printed by a C++ compile of include/fta.h
     assert C.sizeof(_lib.FtaParams) == 496
     assert C.sizeof(_lib.FtaMergeParams) == 64
+    assert C.sizeof(_lib.FtaExchangeParams) == 192
+    assert _lib.FtaExchangeParams.out.offset == 176
+
+
+def test_exchange_merge_arguments_are_validated(fta_lib):
+    """Bad rank counts, ranks and null pointers are refused before anything is launched."""
+    p = _lib.FtaExchangeParams()
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG
+    p.out = p.flag_local = p.status = 4096
+    p.world, p.rank, p.rows, p.D, p.out_dtype, p.timeout_ns = 9, 0, 16, 128, _lib.DTYPE_F32, 1000
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # more than FTA_MAX_RANKS
+    p.world, p.rank = 2, 2
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # rank outside the group
+    p.rank = 0
+    p.part[0] = 4096
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # rank 1's partial missing
+    p.part[1] = 4096
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # no flag address for rank 1
+    p.flag_peer[1] = 4096
+    p.timeout_ns = 0
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # the wait must be bounded
 
 
 def _params(B, H, Hkv, Q, D, ctx, grid, with_tree=1, kernel=_lib.KERNEL_MMA):

@@ -106,3 +106,13 @@ def test_kv_ranges_cover_the_sequence():
             assert r[0][0] == 0 and r[-1][1] == L
             assert all(a[1] == b[0] for a, b in zip(r, r[1:]))
             assert all(lo % 64 == 0 for lo, _ in r if lo < L)
+
+
+def test_exchange_layout_is_aligned_and_disjoint():
+    """Two 16-byte-aligned partial buffers, then one flag per rank, nothing overlapping."""
+    for no, nl, world in [(8 * 64 * 128, 8 * 64, 2), (130, 13, 8), (4, 1, 3)]:
+        from flash_tree_attn_b200 import dist as fdist
+
+        stride, flags, total = fdist.exchange_layout(no, nl, world)
+        assert stride % 4 == 0 and stride >= no + nl
+        assert flags == 2 * stride and total >= flags + world and total % 4 == 0
