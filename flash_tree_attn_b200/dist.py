@@ -113,6 +113,7 @@ class PeerExchange:
         self.epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._keep = []
+        self._params = None
         import os
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -133,27 +134,35 @@ class PeerExchange:
         off = ((self.epoch + 1) & 1) * self.stride
         return self.local[off:off + self.no], self.local[off + self.no:off + self.no + self.nl]
 
-    def merge(self, o_shape, lse_shape, out_dtype: torch.dtype):
-        """Signal, wait for the peers, merge all ranks' partials: (out, lse) on this rank."""
+    def merge(self, o_shape, lse_shape, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
+              lse: Optional[torch.Tensor] = None):
+        """Signal, wait for the peers, merge all ranks' partials: (out, lse) on this rank, written
+        into `out` / `lse` (contiguous, of `out_dtype` / fp32) when given."""
         from . import _lib
         from .op import _DT
 
         self.epoch += 1
         D = int(o_shape[-1])
-        rows = self.nl
-        assert rows * D == self.no
-        out = torch.empty(tuple(o_shape), dtype=out_dtype, device=self.device)
-        lse = torch.empty(tuple(lse_shape), dtype=torch.float32, device=self.device)
-        p = _lib.FtaExchangeParams()
+        assert self.nl * D == self.no
+        if out is None:
+            out = torch.empty(tuple(o_shape), dtype=out_dtype, device=self.device)
+        if lse is None:
+            lse = torch.empty(tuple(lse_shape), dtype=torch.float32, device=self.device)
+        assert out.is_contiguous() and lse.is_contiguous() and out.dtype == out_dtype and lse.dtype == torch.float32
+        p = self._params
+        if p is None:
+            p = self._params = _lib.FtaExchangeParams()
+            for s in range(self.world):
+                p.flag_peer[s] = self.base[s] + (self.flags_off + self.rank) * 4
+            p.flag_local = self.base[self.rank] + self.flags_off * 4
+            p.status = self.status.data_ptr()
+            p.timeout_ns = self.timeout_ns
+            p.world, p.rank, p.rows = self.world, self.rank, self.nl
         off = (self.epoch & 1) * self.stride * 4
         for s in range(self.world):
             p.part[s] = self.base[s] + off
-            p.flag_peer[s] = self.base[s] + (self.flags_off + self.rank) * 4
-        p.flag_local = self.base[self.rank] + self.flags_off * 4
-        p.status = self.status.data_ptr()
-        p.timeout_ns = self.timeout_ns
-        p.world, p.rank, p.epoch = self.world, self.rank, self.epoch & 0xFFFFFFFF
-        p.rows, p.D, p.out_dtype = rows, D, _DT[out_dtype]
+        p.epoch = self.epoch & 0xFFFFFFFF
+        p.D, p.out_dtype = D, _DT[out_dtype]
         p.out, p.lse = out.data_ptr(), lse.data_ptr()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.load().fta_exchange_merge(C.byref(p), stream), "fta_exchange_merge")
@@ -172,6 +181,38 @@ class PeerExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         self._keep.clear()
+
+
+class PreparedKvRange:
+    """`kv_range_decode` through a PeerExchange, validated once: the operator call is prepared
+    for each of the exchange's two buffers, the result tensors are allocated here, and `run()` is
+    three launches (stage 1, stage 2, exchange-merge) with no other host work.  The input tensors
+    may be overwritten in place between runs; every rank calls `run()` the same number of times.
+    """
+
+    def __init__(self, q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size: int = 64,
+                 kv_group_num: int = 1, *, exchange: "PeerExchange", out_dtype: Optional[torch.dtype] = None):
+        from .op import prepare
+
+        B, H, Q, D = q.shape
+        x = self.exchange = exchange
+        assert x.no == B * H * Q * D and x.nl == B * H * Q
+        self.calls = []
+        for parity in (0, 1):
+            off = parity * x.stride
+            self.calls.append(prepare(
+                q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size, None, kv_group_num=kv_group_num,
+                want_lse=True, out_dtype=torch.float32, with_tree=x.rank == x.world - 1,
+                out_buf=x.local[off:off + x.no].view(B, H, Q, D), lse_buf=x.local[off + x.no:off + x.no + x.nl].view(B, H, Q)))
+        self.out_dtype = out_dtype or q.dtype
+        self.out = torch.empty((B, H, Q, D), dtype=self.out_dtype, device=q.device)
+        self.lse = torch.empty((B, H, Q), dtype=torch.float32, device=q.device)
+        self.launches = 3
+
+    def run(self):
+        x = self.exchange
+        self.calls[(x.epoch + 1) & 1].run()
+        return x.merge(self.out.shape, self.lse.shape, self.out_dtype, out=self.out, lse=self.lse)
 
 
 def kv_range_decode(

@@ -51,6 +51,18 @@ def main():
         worst = max(worst, float(o_x.float().abs().max()))
     assert worst > 0.0 and torch.isfinite(o_x.float()).all()
 
+    # the prepared form gives the same bits, run after run, interleaved with plain calls
+    prep = fdist.PreparedKvRange(inp["q"], k_sh, v_sh, inp["current_k"], inp["current_v"], inp["mask"], shard_len,
+                                 w.block_size, w.G, exchange=xch)
+    o_ref, l_ref = call(inp["q"], None)
+    for i in range(5):
+        o_p, l_p = prep.run()
+        assert torch.equal(o_ref, o_p) and torch.equal(l_ref, l_p), f"rank {rank}: prepared run {i} differs"
+        if i == 2:
+            o_x, _ = call(inp["q"], xch)
+            assert torch.equal(o_ref, o_x)
+    xch.check()
+
     def timed(exchange, n=30):
         for _ in range(5):
             call(inp["q"], exchange)
@@ -65,10 +77,22 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0]) * 1e3
 
-    us_nccl, us_x = timed(None), timed(xch)
+    def timed_prepared(n=30):
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            prep.run()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]) * 1e3
+
+    us_nccl, us_x, us_p = timed(None), timed(xch), timed_prepared()
     xch.check()
     print(f"EXCHANGE_OK rank {rank}/{world} ctx {ctx}: all-gather+merge {us_nccl:.1f} us/call, "
-          f"exchange-merge {us_x:.1f} us/call", flush=True)
+          f"exchange-merge {us_x:.1f} us/call, prepared {us_p:.1f} us/call", flush=True)
     xch.close()
     dist.barrier()
     dist.destroy_process_group()
