@@ -177,8 +177,9 @@ def seq_split_arm(args, w, fta, dev, rank, world, dist):
     shard_len = torch.tensor([max(0, min(lens[0], hi) - lo)], dtype=torch.int32, device=dev)
 
     xch = None
-    if args.exchange == "peer":
-        xch = fdist.PeerExchange(w.B * w.H * w.Q * w.D, w.B * w.H * w.Q, dev)
+    if args.exchange != "nccl":
+        form = {"peer": "auto", "peer-gather": "gather", "peer-scatter": "scatter"}[args.exchange]
+        xch = fdist.PeerExchange(w.B * w.H * w.Q * w.D, w.B * w.H * w.Q, dev, form=form)
 
     def step(q, ck, cv, mask):
         return fdist.kv_range_decode(q, k_sh, v_sh, ck, cv, mask, shard_len, w.block_size, w.G, exchange=xch)
@@ -240,7 +241,8 @@ def seq_split_arm(args, w, fta, dev, rank, world, dist):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload_config(w, lens), parallelism=f"kv-range x{world}, " + (
-                "one exchange-merge kernel per call over peer-mapped memory" if xch is not None
+                f"one exchange-merge kernel per call over peer-mapped memory ({'scatter' if xch.scatter else 'gather'} form)"
+                if xch is not None
                 else "one all-gather + merge per call")),
             "kv_read_gbs": kvb * calls_s / 1e9, "tflops": tfl,
             "roofline": {"bound": "tensor", "achieved": tfl, "peak": tf_peak * world, "unit": "TFLOP/s",
@@ -284,9 +286,11 @@ def main():
     ap.add_argument("--paged", type=int, default=0, metavar="PAGE_SIZE",
                     help="house the KV cache in shuffled pages of this many rows (multiple of 64) and "
                          "run the device-timed region through the block table (implies --skip-e2e)")
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+    ap.add_argument("--exchange", choices=["peer", "peer-gather", "peer-scatter", "nccl"], default="peer",
                     help="sequence-split arm (one long sequence on several GPUs): 'peer' = one exchange-merge "
-                         "kernel per rank over peer-mapped memory, 'nccl' = all-gather + merge kernel")
+                         "kernel per rank over peer-mapped memory (-gather: every rank reads all partials; "
+                         "-scatter: every rank merges a slice of the rows and stores it to all; plain 'peer' "
+                         "takes the library's choice), 'nccl' = all-gather + merge kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

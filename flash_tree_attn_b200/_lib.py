@@ -89,7 +89,8 @@ class FtaExchangeParams(C.Structure):
 
     _fields_ = [
         ("part", _vp * FTA_MAX_RANKS), ("flag_peer", _vp * FTA_MAX_RANKS),
-        ("flag_local", _vp), ("status", _vp), ("timeout_ns", _i64),
+        ("out_peer", _vp * FTA_MAX_RANKS), ("lse_peer", _vp * FTA_MAX_RANKS),
+        ("flag_local", _vp), ("status", _vp), ("done", _vp), ("timeout_ns", _i64),
         ("world", _i32), ("rank", _i32), ("epoch", C.c_uint32), ("rows", _i32), ("D", _i32), ("out_dtype", _i32),
         ("out", _vp), ("lse", _vp),
     ]

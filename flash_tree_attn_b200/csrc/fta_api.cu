@@ -298,13 +298,16 @@ int fta_merge_parts(const FtaMergeParams* p, void* stream) {
 }
 
 int fta_exchange_merge(const FtaExchangeParams* p, void* stream) {
-  if (!p || !p->out || !p->flag_local || !p->status) return FTA_E_BADARG;
+  if (!p || !p->flag_local || !p->status) return FTA_E_BADARG;
   if (p->world < 1 || p->world > FTA_MAX_RANKS || p->rank < 0 || p->rank >= p->world) return FTA_E_BADARG;
   if (p->rows < 0 || p->D < 4 || p->D % 4 != 0 || p->timeout_ns <= 0) return FTA_E_BADARG;
-  if (p->out_dtype < FTA_DTYPE_F16 || p->out_dtype > FTA_DTYPE_F32 || !aligned(p->out, 16)) return FTA_E_BADARG;
+  if (p->out_dtype < FTA_DTYPE_F16 || p->out_dtype > FTA_DTYPE_F32) return FTA_E_BADARG;
+  const bool scatter = p->done != nullptr;
+  if (!scatter && (!p->out || !aligned(p->out, 16))) return FTA_E_BADARG;
   for (int s = 0; s < p->world; ++s) {
     if (!p->part[s] || !aligned(p->part[s], 16)) return FTA_E_BADARG;
     if (s != p->rank && (!p->flag_peer[s] || !aligned(p->flag_peer[s], 4))) return FTA_E_BADARG;
+    if (scatter && (!p->out_peer[s] || !aligned(p->out_peer[s], 16) || !p->lse_peer[s])) return FTA_E_BADARG;
   }
   if (p->rows == 0) return FTA_OK;
   cudaError_t e = fta_launch_exchange_merge(*p, (cudaStream_t)stream);

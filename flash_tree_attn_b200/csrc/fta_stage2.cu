@@ -169,26 +169,54 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
-__global__ void __launch_bounds__(kThreads) exchange_merge_kernel(const FtaExchangeParams p) {
-  __shared__ int s_fail;
+// Threads 1..world of the block (one per peer): tell the peer (when `signal`) and wait until the
+// peer has told us; `slot` selects the first or the second flag round.  Returns through *fail a
+// bit per peer whose signal did not come within the limit.
+__device__ __forceinline__ void exchange_round(const FtaExchangeParams& p, int slot, bool signal, int* fail) {
   const int t = threadIdx.x;
-  if (t == 0) s_fail = 0;
-  __syncthreads();
   if (t < p.world && t != p.rank) {
-    if (blockIdx.x == 0) {
+    if (signal) {
       __threadfence_system();
-      st_release_sys(p.flag_peer[t], p.epoch);
+      st_release_sys(p.flag_peer[t] + slot * p.world, p.epoch);
     }
+    const unsigned* mine = p.flag_local + slot * p.world + t;
     const unsigned long long t0 = global_ns();
     unsigned spins = 0;
-    while ((int)(ld_acquire_sys(p.flag_local + t) - p.epoch) < 0) {
+    while ((int)(ld_acquire_sys(mine) - p.epoch) < 0) {
       if ((++spins & 31u) == 0 && global_ns() - t0 > (unsigned long long)p.timeout_ns) {
-        atomicOr(&s_fail, 1 << t);
+        atomicOr(fail, 1 << (t + 8 * slot));
         break;
       }
       __nanosleep(32);
     }
   }
+}
+
+// Folds rank 0..world-1's partials of one float4 of one row, in rank order.
+__device__ __forceinline__ Acc exchange_fold(const FtaExchangeParams& p, long long row, int c4) {
+  const long long lse_off = (long long)p.rows * p.D;
+  float lse[FTA_MAX_RANKS];
+  float4 o[FTA_MAX_RANKS];
+#pragma unroll
+  for (int s = 0; s < FTA_MAX_RANKS; ++s)
+    if (s < p.world) {
+      lse[s] = __ldcg(p.part[s] + lse_off + row);
+      o[s] = __ldcg(reinterpret_cast<const float4*>(p.part[s] + row * p.D + c4));
+    }
+  Acc acc; acc.init();
+#pragma unroll
+  for (int s = 0; s < FTA_MAX_RANKS; ++s)
+    if (s < p.world) acc.add(lse[s], o[s]);
+  return acc;
+}
+
+// Every rank reads every peer's whole partial and merges all rows itself: one flag round.
+__global__ void __launch_bounds__(kThreads) exchange_merge_kernel(const FtaExchangeParams p) {
+  __shared__ int s_fail;
+  const int t = threadIdx.x;
+  if (t == 0) s_fail = 0;
+  __syncthreads();
+  exchange_round(p, 0, blockIdx.x == 0, &s_fail);
   __syncthreads();
   if (s_fail) {
     if (t == 0) atomicOr(p.status, s_fail);
@@ -196,35 +224,84 @@ __global__ void __launch_bounds__(kThreads) exchange_merge_kernel(const FtaExcha
   }
   const int D4 = p.D >> 2;
   const long long n = (long long)p.rows * D4;
-  const long long lse_off = (long long)p.rows * p.D;
   for (long long i = (long long)blockIdx.x * kThreads + t; i < n; i += (long long)gridDim.x * kThreads) {
     const long long row = i / D4;
     const int c4 = (int)(i - row * D4) * 4;
-    float lse[FTA_MAX_RANKS];
-    float4 o[FTA_MAX_RANKS];
-#pragma unroll
-    for (int s = 0; s < FTA_MAX_RANKS; ++s)
-      if (s < p.world) {
-        lse[s] = __ldcg(p.part[s] + lse_off + row);
-        o[s] = __ldcg(reinterpret_cast<const float4*>(p.part[s] + row * p.D + c4));
-      }
-    Acc acc; acc.init();
-#pragma unroll
-    for (int s = 0; s < FTA_MAX_RANKS; ++s)
-      if (s < p.world) acc.add(lse[s], o[s]);
+    const Acc acc = exchange_fold(p, row, c4);
     fta_store4(p.out, p.out_dtype, row * p.D + c4, acc.value());
     if (c4 == 0 && p.lse) p.lse[row] = acc.lse();
   }
 }
 
+// With many ranks reading everything from everybody is an all-gather of the fp32 partials
+// ((world - 1) x the partial over NVLink into every GPU).  Here each rank merges only ITS slice of
+// the rows (reads 1/world of every peer's partial) and stores the merged, rounded rows into every
+// rank's result buffer (peer-mapped as well): about (world - 1) / world of ONE partial in and half
+// of that out per GPU.  Two flag rounds: "my partial is ready", then, from the last block to finish
+// its stores, "my slice is in your result buffer"; the kernel ends when every peer's slice is in.
+//   * Nobody stores into a peer's result buffer before that peer has signalled the first round of
+//     this call, i.e. before the peer's stream has passed everything that read the previous result.
+//   * p.done counts finished blocks and is set back to zero by the last one.
+__global__ void __launch_bounds__(kThreads) exchange_scatter_kernel(const FtaExchangeParams p) {
+  __shared__ int s_fail, s_last;
+  const int t = threadIdx.x;
+  if (t == 0) s_fail = 0;
+  __syncthreads();
+  exchange_round(p, 0, blockIdx.x == 0, &s_fail);
+  __syncthreads();
+  if (s_fail) {
+    if (t == 0) atomicOr(p.status, s_fail);
+  } else {
+    const int D4 = p.D >> 2;
+    const int per = (p.rows + p.world - 1) / p.world;
+    const int r0 = min(p.rows, p.rank * per), r1 = min(p.rows, r0 + per);
+    const long long n = (long long)(r1 - r0) * D4;
+    for (long long i = (long long)blockIdx.x * kThreads + t; i < n; i += (long long)gridDim.x * kThreads) {
+      const long long row = r0 + i / D4;
+      const int c4 = (int)(i % D4) * 4;
+      const Acc acc = exchange_fold(p, row, c4);
+      const float4 v = acc.value();
+      const float l = acc.lse();
+#pragma unroll
+      for (int s = 0; s < FTA_MAX_RANKS; ++s)
+        if (s < p.world) {
+          fta_store4(p.out_peer[s], p.out_dtype, row * p.D + c4, v);
+          if (c4 == 0) p.lse_peer[s][row] = l;
+        }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (t == 0) {
+    s_last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
+    __threadfence();
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (t == 0) {
+    *p.done = 0;
+    s_fail = *reinterpret_cast<volatile int*>(p.status);  // some block of this launch gave up: no second round
+  }
+  __syncthreads();
+  if (s_fail) return;
+  exchange_round(p, 1, true, &s_fail);
+  __syncthreads();
+  if (t == 0 && s_fail) atomicOr(p.status, s_fail);
+}
+
 }  // namespace
 
 cudaError_t fta_launch_exchange_merge(const FtaExchangeParams& p, cudaStream_t st) {
-  const long long n = (long long)p.rows * (p.D >> 2);
+  const bool scatter = p.done != nullptr;
+  const long long rows = scatter ? (p.rows + p.world - 1) / p.world : p.rows;
+  const long long n = rows * (p.D >> 2);
   long long blocks = (n + kThreads - 1) / kThreads;
   if (blocks > 148 * 4) blocks = 148 * 4;
   if (blocks < 1) blocks = 1;
-  exchange_merge_kernel<<<(int)blocks, kThreads, 0, st>>>(p);
+  if (scatter)
+    exchange_scatter_kernel<<<(int)blocks, kThreads, 0, st>>>(p);
+  else
+    exchange_merge_kernel<<<(int)blocks, kThreads, 0, st>>>(p);
   return cudaGetLastError();
 }
 

@@ -19,7 +19,7 @@ operator and `fta_merge_parts`.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import Callable, List, NamedTuple, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -79,48 +79,68 @@ def _default_merge(po, pl, out_dtype):
     return merge_partials(po, pl, out_dtype)
 
 
-def exchange_layout(numel_o: int, numel_lse: int, world: int) -> Tuple[int, int, int]:
-    """Per-rank layout of the peer-mapped allocation, in 4-byte words: two packed partial
-    buffers (each [numel_o + numel_lse] fp32 rounded up to 16 bytes) then `world` uint32 flags.
-    Returns (buffer_stride, flags_offset, total)."""
-    stride = -(-(numel_o + numel_lse) // 4) * 4
-    flags = 2 * stride
-    return stride, flags, flags + -(-world // 4) * 4
+class ExchangeLayout(NamedTuple):
+    """Offsets, in 4-byte words, inside one rank's peer-mapped allocation."""
+    stride: int   # distance between the two packed partial buffers (each [numel_o + numel_lse] fp32)
+    out: int      # merged result, numel_o elements of up to 4 bytes
+    lse: int      # merged LSE, numel_lse fp32
+    flags: int    # 2 * world uint32: first-round flags, then second-round flags
+    total: int
+
+
+def exchange_layout(numel_o: int, numel_lse: int, world: int) -> ExchangeLayout:
+    """Every region starts on a 16-byte boundary."""
+    up = lambda n: -(-n // 4) * 4
+    stride = up(numel_o + numel_lse)
+    out = 2 * stride
+    lse = out + up(numel_o)
+    flags = lse + up(numel_lse)
+    return ExchangeLayout(stride, out, lse, flags, flags + up(2 * world))
 
 
 class PeerExchange:
-    """Peer-mapped partial buffers and flags of the ranks of one box, for `fta_exchange_merge`.
+    """Peer-mapped partial buffers, result buffer and flags of the ranks of one box, for
+    `fta_exchange_merge`.
 
     Construction is collective (every rank of `group`, same arguments).  The memory comes from
     torch.distributed._symmetric_memory: one allocation per rank, mapped into every peer by its
     rendezvous; only plain peer loads and stores are used on it.
+    `form`: "gather" (every rank reads all partials and merges all rows; the results are new
+    tensors), "scatter" (every rank merges its slice of the rows and stores it into every rank's
+    result buffer; the results are views of that buffer, overwritten by the next call), or
+    "auto": the gather form, the faster one where both were measured.
     The calls `mine()` ... `merge()` must come in the same order on every rank; the object counts
-    the epoch and alternates between the two buffers itself.
+    the epoch and alternates between the two partial buffers itself.
     """
 
     def __init__(self, numel_o: int, numel_lse: int, device: torch.device, group: Optional[dist.ProcessGroup] = None,
-                 timeout_s: float = 1.0):
+                 timeout_s: float = 1.0, form: str = "auto"):
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
         from . import _lib
 
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         if self.world > _lib.FTA_MAX_RANKS:
             raise ValueError(f"at most {_lib.FTA_MAX_RANKS} ranks")
+        if form not in ("auto", "gather", "scatter"):
+            raise ValueError(form)
+        self.scatter = form == "scatter"
         self.no, self.nl = int(numel_o), int(numel_lse)
-        self.stride, self.flags_off, total = exchange_layout(self.no, self.nl, self.world)
+        self.layout = exchange_layout(self.no, self.nl, self.world)
+        self.stride = self.layout.stride
         self.device = torch.device(device)
         self.timeout_ns = int(timeout_s * 1e9)
         self.epoch = 0
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._words = torch.zeros(2, dtype=torch.int32, device=self.device)  # status, finished-block count
+        self.status = self._words[:1]
         self._keep = []
         self._params = None
-        import os
-
-        import torch.distributed._symmetric_memory as symm_mem
-
         # plain peer mappings only: no NVLink multicast object is bound to this memory
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        self.local = symm_mem.empty(total, dtype=torch.float32, device=self.device)
+        self.local = symm_mem.empty(self.layout.total, dtype=torch.float32, device=self.device)
         self.local.zero_()
         hdl = symm_mem.rendezvous(self.local, self.group)
         self.base = [int(x) for x in hdl.buffer_ptrs]
@@ -136,26 +156,37 @@ class PeerExchange:
 
     def merge(self, o_shape, lse_shape, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
               lse: Optional[torch.Tensor] = None):
-        """Signal, wait for the peers, merge all ranks' partials: (out, lse) on this rank, written
-        into `out` / `lse` (contiguous, of `out_dtype` / fp32) when given."""
+        """Signal, wait for the peers, merge all ranks' partials: (out, lse) on this rank.
+        Gather form: written into `out` / `lse` (contiguous, of `out_dtype` / fp32) when given, else
+        into new tensors.  Scatter form: views of this rank's peer-mapped result buffer, valid until
+        the next merge(); `out` / `lse` are not used."""
         from . import _lib
         from .op import _DT
 
         self.epoch += 1
         D = int(o_shape[-1])
         assert self.nl * D == self.no
-        if out is None:
-            out = torch.empty(tuple(o_shape), dtype=out_dtype, device=self.device)
-        if lse is None:
-            lse = torch.empty(tuple(lse_shape), dtype=torch.float32, device=self.device)
-        assert out.is_contiguous() and lse.is_contiguous() and out.dtype == out_dtype and lse.dtype == torch.float32
+        L = self.layout
+        if self.scatter:
+            out = self.local[L.out:L.out + self.no].view(out_dtype)[:self.no].view(tuple(o_shape))
+            lse = self.local[L.lse:L.lse + self.nl].view(tuple(lse_shape))
+        else:
+            if out is None:
+                out = torch.empty(tuple(o_shape), dtype=out_dtype, device=self.device)
+            if lse is None:
+                lse = torch.empty(tuple(lse_shape), dtype=torch.float32, device=self.device)
+            assert out.is_contiguous() and lse.is_contiguous() and out.dtype == out_dtype and lse.dtype == torch.float32
         p = self._params
         if p is None:
             p = self._params = _lib.FtaExchangeParams()
             for s in range(self.world):
-                p.flag_peer[s] = self.base[s] + (self.flags_off + self.rank) * 4
-            p.flag_local = self.base[self.rank] + self.flags_off * 4
-            p.status = self.status.data_ptr()
+                p.flag_peer[s] = self.base[s] + (L.flags + self.rank) * 4
+                if self.scatter:
+                    p.out_peer[s] = self.base[s] + L.out * 4
+                    p.lse_peer[s] = self.base[s] + L.lse * 4
+            p.flag_local = self.base[self.rank] + L.flags * 4
+            p.status = self._words.data_ptr()
+            p.done = self._words.data_ptr() + 4 if self.scatter else None
             p.timeout_ns = self.timeout_ns
             p.world, p.rank, p.rows = self.world, self.rank, self.nl
         off = (self.epoch & 1) * self.stride * 4
@@ -163,7 +194,8 @@ class PeerExchange:
             p.part[s] = self.base[s] + off
         p.epoch = self.epoch & 0xFFFFFFFF
         p.D, p.out_dtype = D, _DT[out_dtype]
-        p.out, p.lse = out.data_ptr(), lse.data_ptr()
+        if not self.scatter:
+            p.out, p.lse = out.data_ptr(), lse.data_ptr()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.load().fta_exchange_merge(C.byref(p), stream), "fta_exchange_merge")
         return out, lse
@@ -173,7 +205,7 @@ class PeerExchange:
         st = int(self.status.item())
         if st:
             self.status.zero_()
-            late = [s for s in range(self.world) if st >> s & 1]
+            late = sorted({s for s in range(self.world) if (st >> s & 1) or (st >> (8 + s) & 1)})
             raise TimeoutError(f"rank {self.rank}: no signal from rank(s) {late} within {self.timeout_ns / 1e9:.1f} s")
 
     def close(self) -> None:
@@ -205,14 +237,18 @@ class PreparedKvRange:
                 want_lse=True, out_dtype=torch.float32, with_tree=x.rank == x.world - 1,
                 out_buf=x.local[off:off + x.no].view(B, H, Q, D), lse_buf=x.local[off + x.no:off + x.no + x.nl].view(B, H, Q)))
         self.out_dtype = out_dtype or q.dtype
-        self.out = torch.empty((B, H, Q, D), dtype=self.out_dtype, device=q.device)
-        self.lse = torch.empty((B, H, Q), dtype=torch.float32, device=q.device)
+        self.o_shape, self.lse_shape = (B, H, Q, D), (B, H, Q)
+        self.out = self.lse = None
+        if not x.scatter:
+            self.out = torch.empty(self.o_shape, dtype=self.out_dtype, device=q.device)
+            self.lse = torch.empty(self.lse_shape, dtype=torch.float32, device=q.device)
         self.launches = 3
 
     def run(self):
+        """(out, lse); the same tensors every time, overwritten by the next run."""
         x = self.exchange
         self.calls[(x.epoch + 1) & 1].run()
-        return x.merge(self.out.shape, self.lse.shape, self.out_dtype, out=self.out, lse=self.lse)
+        return x.merge(self.o_shape, self.lse_shape, self.out_dtype, out=self.out, lse=self.lse)
 
 
 def kv_range_decode(
@@ -237,7 +273,9 @@ def kv_range_decode(
         mo, ml = exchange.mine()
         decode_fn(q, k_shard, v_shard, current_k, current_v, mask, shard_len, block_size, kv_group_num,
                   rank == world - 1, out_buf=mo.view(B, H, Q, D), lse_buf=ml.view(B, H, Q))
-        return exchange.merge((B, H, Q, D), (B, H, Q), out_dtype or q.dtype)
+        out, lse = exchange.merge((B, H, Q, D), (B, H, Q), out_dtype or q.dtype)
+        # scatter form: the result sits in the exchange's buffer and the next call overwrites it
+        return (out.clone(), lse.clone()) if exchange.scatter else (out, lse)
     if decode_fn is _default_decode:
         # the operator writes its partial straight into this rank's slot of the packed buffer
         no, nl = B * H * Q * D, B * H * Q

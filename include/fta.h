@@ -163,19 +163,34 @@ typedef struct FtaMergeParams {
  *                 rows floats of LSE; part[rank] is this rank's own.  Peer entries are device
  *                 pointers of memory mapped from the peer (cuMemMap of an exported handle).
  *   flag_peer[s]  address, as mapped here, of element [rank] of rank s's flag array
- *   flag_local    this rank's flag array [world] (uint32, zero before the first call)
+ *   flag_local    this rank's flag array [2 * world] (uint32, zero before the first call);
+ *                 elements [world, 2 * world) serve the second round of the scatter form
  *   epoch         1, 2, 3, ... (mod 2^32) the same on every rank for the same call
- *   status        device word; bit s is set when the wait for rank s ran out (nothing is stored)
- *   timeout_ns    bound of that wait
+ *   status        device word; bit s is set when the wait for rank s ran out (bit 8 + s: in the
+ *                 second round); what was stored by then is not a result
+ *   timeout_ns    bound of each wait
+ * Two forms.
+ *   done == NULL ("gather"): every rank reads every peer's whole partial and writes all rows of
+ *     out / lse, which are private to the rank.  One flag round.
+ *   done != NULL ("scatter"): rank r merges rows [r * ceil(rows / world), ...) only and stores
+ *     them into EVERY rank's result through out_peer[s] / lse_peer[s] (rank s's result buffers as
+ *     mapped here; entry [rank] is this rank's own; out and lse are not used); a second flag
+ *     round tells the peers that the slice has arrived.  `done` is a zeroed device int32 private
+ *     to the rank.  Less NVLink traffic with many ranks: one partial in and half a result out per
+ *     GPU instead of (world - 1) partials in.
  * The caller alternates between two partial buffers from call to call (a peer may still read the
- * previous one) and makes the calls in the same order on every rank.
+ * previous one) and makes the calls in the same order on every rank.  One result buffer per rank
+ * is enough: a peer stores into it only after this rank has entered the same call.
  */
 #define FTA_MAX_RANKS 8
 typedef struct FtaExchangeParams {
   const float* part[FTA_MAX_RANKS];
   uint32_t* flag_peer[FTA_MAX_RANKS];
+  void* out_peer[FTA_MAX_RANKS];
+  float* lse_peer[FTA_MAX_RANKS];
   const uint32_t* flag_local;
   int32_t* status;
+  int32_t* done;
   int64_t timeout_ns;
   int32_t world;
   int32_t rank;

@@ -4,7 +4,8 @@ Every rank owns a contiguous KV range of one long sequence.  The same call goes 
 path (all-gather of the packed partials, then fta_merge_parts) and through fta_exchange_merge over
 peer-mapped memory; both fold the ranks' partials in rank order with the same arithmetic, so the
 results must be identical bit for bit, many calls in a row (two alternating buffers, growing
-epochs).  Prints one line "EXCHANGE_OK ..." per rank on success.
+epochs).  Both forms of the exchange are run.  Prints one line "EXCHANGE_OK <form> ..." per rank and form
+on success.
 """
 import os
 import sys
@@ -33,7 +34,15 @@ def main():
     k_sh, v_sh = inp["k_cache"][:, :, lo:hi], inp["v_cache"][:, :, lo:hi]
     shard_len = torch.tensor([hi - lo], dtype=torch.int32, device=dev)
     B, H, Q, D = inp["q"].shape
-    xch = fdist.PeerExchange(B * H * Q * D, B * H * Q, dev, timeout_s=2.0)
+    for form in ("gather", "scatter"):
+        one_form(form, fdist, dist, inp, w, k_sh, v_sh, shard_len, dev, rank, world, ctx, iters)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def one_form(form, fdist, dist, inp, w, k_sh, v_sh, shard_len, dev, rank, world, ctx, iters):
+    B, H, Q, D = inp["q"].shape
+    xch = fdist.PeerExchange(B * H * Q * D, B * H * Q, dev, timeout_s=2.0, form=form)
 
     def call(q, exchange):
         return fdist.kv_range_decode(q, k_sh, v_sh, inp["current_k"], inp["current_v"], inp["mask"], shard_len,
@@ -61,6 +70,7 @@ def main():
         if i == 2:
             o_x, _ = call(inp["q"], xch)
             assert torch.equal(o_ref, o_x)
+            o_p, l_p = None, None  # (scatter form: the views were overwritten by that call)
     xch.check()
 
     def timed(exchange, n=30):
@@ -91,11 +101,9 @@ def main():
 
     us_nccl, us_x, us_p = timed(None), timed(xch), timed_prepared()
     xch.check()
-    print(f"EXCHANGE_OK rank {rank}/{world} ctx {ctx}: all-gather+merge {us_nccl:.1f} us/call, "
+    print(f"EXCHANGE_OK {form} rank {rank}/{world} ctx {ctx}: all-gather+merge {us_nccl:.1f} us/call, "
           f"exchange-merge {us_x:.1f} us/call, prepared {us_p:.1f} us/call", flush=True)
     xch.close()
-    dist.barrier()
-    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

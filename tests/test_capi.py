@@ -37,8 +37,8 @@ def test_struct_layout_matches_header():
     # sizes printed by a C++ compile of include/fta.h
     assert C.sizeof(_lib.FtaParams) == 496
     assert C.sizeof(_lib.FtaMergeParams) == 64
-    assert C.sizeof(_lib.FtaExchangeParams) == 192
-    assert _lib.FtaExchangeParams.out.offset == 176
+    assert C.sizeof(_lib.FtaExchangeParams) == 328
+    assert _lib.FtaExchangeParams.out.offset == 312
 
 
 def test_exchange_merge_arguments_are_validated(fta_lib):
@@ -58,6 +58,11 @@ def test_exchange_merge_arguments_are_validated(fta_lib):
     p.flag_peer[1] = 4096
     p.timeout_ns = 0
     assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # the wait must be bounded
+    p.timeout_ns = 1000
+    p.done = 4096  # scatter form: every rank's result buffers must be given
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG
+    p.out_peer[0] = p.out_peer[1] = p.lse_peer[0] = 4096
+    assert fta_lib.fta_exchange_merge(C.byref(p), None) == _lib.FTA_E_BADARG  # rank 1's LSE buffer missing
 
 
 def _params(B, H, Hkv, Q, D, ctx, grid, with_tree=1, kernel=_lib.KERNEL_MMA):

@@ -109,10 +109,12 @@ def test_kv_ranges_cover_the_sequence():
 
 
 def test_exchange_layout_is_aligned_and_disjoint():
-    """Two 16-byte-aligned partial buffers, then one flag per rank, nothing overlapping."""
-    for no, nl, world in [(8 * 64 * 128, 8 * 64, 2), (130, 13, 8), (4, 1, 3)]:
-        from flash_tree_attn_b200 import dist as fdist
+    """Two partial buffers, the result, its LSE and two flags per rank: every region on a 16-byte
+    boundary, nothing overlapping."""
+    from flash_tree_attn_b200 import dist as fdist
 
-        stride, flags, total = fdist.exchange_layout(no, nl, world)
-        assert stride % 4 == 0 and stride >= no + nl
-        assert flags == 2 * stride and total >= flags + world and total % 4 == 0
+    for no, nl, world in [(8 * 64 * 128, 8 * 64, 2), (130, 13, 8), (4, 1, 3)]:
+        L = fdist.exchange_layout(no, nl, world)
+        assert all(x % 4 == 0 for x in L)
+        assert L.stride >= no + nl and L.out == 2 * L.stride
+        assert L.lse >= L.out + no and L.flags >= L.lse + nl and L.total >= L.flags + 2 * world
