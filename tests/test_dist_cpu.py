@@ -33,6 +33,83 @@ def _oracle_merge(po, pl, out_dtype):
     return o.to(out_dtype), l
 
 
+def _oracle_decode_into(q, k, v, ck, cv, mask, lens, block_size, G, with_tree, out_buf=None, lse_buf=None):
+    o, l = _oracle_decode(q, k, v, ck, cv, mask, lens, block_size, G, with_tree)
+    out_buf.copy_(o)
+    lse_buf.copy_(l)
+
+
+class _GlooExchange:
+    """Stand-in that follows PeerExchange's host protocol (epoch count, two alternating partial
+    buffers, mine() before merge()); the peers' buffers are reached by a gloo all-gather instead of
+    mapped memory.  A buffer is poisoned once merged, so a call that read a stale one would show."""
+
+    scatter = False
+
+    def __init__(self, no, nl):
+        self.no, self.nl, self.epoch = no, nl, 0
+        self.buf = torch.full((2, no + nl), float("nan"))
+
+    def mine(self):
+        b = self.buf[(self.epoch + 1) & 1]
+        return b[:self.no], b[self.no:]
+
+    def merge(self, o_shape, lse_shape, out_dtype, out=None, lse=None):
+        from oracle.tree_attention_oracle import merge_partials_oracle
+
+        self.epoch += 1
+        mine = self.buf[self.epoch & 1]
+        every = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(every, mine.clone())
+        mine.fill_(float("nan"))
+        po = torch.stack([e[:self.no].view(tuple(o_shape)) for e in every])
+        pl = torch.stack([e[self.no:].view(tuple(lse_shape)) for e in every])
+        o, l = merge_partials_oracle(po, pl)
+        return o.to(out_dtype), l
+
+
+def _exchange_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        from flash_tree_attn_b200.dist import kv_range_decode, kv_ranges
+        from oracle.tree_attention_oracle import tree_attention_oracle
+
+        g = load_golden("cfg1")
+        lens = g["kv_seq_len"]
+        lo, hi = kv_ranges(g["k_cache"].size(2), world, align=16)[rank]
+        shard_len = torch.clamp(lens - lo, min=0, max=hi - lo).to(torch.int32)
+        B, H, Q, D = g["q"].shape
+        xch = _GlooExchange(B * H * Q * D, B * H * Q)
+        worst = 0.0
+        for call in range(3):  # consecutive calls alternate between the two buffers
+            q = g["q"].float() * (1.0 + 0.25 * call)
+            out, lse = kv_range_decode(q, g["k_cache"][:, :, lo:hi], g["v_cache"][:, :, lo:hi], g["current_k"],
+                                       g["current_v"], g["mask"], shard_len, 64, 1, out_dtype=torch.float32,
+                                       decode_fn=_oracle_decode_into, exchange=xch)
+            whole = tree_attention_oracle(q, g["k_cache"], g["v_cache"], g["current_k"], g["current_v"], g["mask"],
+                                          lens, None, 1)
+            worst = max(worst, (out - whole["out"]).abs().max().item(), (lse - whole["lse"]).abs().max().item())
+        ret[rank] = (worst, xch.epoch)
+    except Exception as e:
+        ret[rank] = repr(e)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_range_decode_through_an_exchange_object_two_ranks():
+    """The exchange branch of kv_range_decode: the operator writes into the exchange's current
+    buffer, merge() finishes the call, three calls in a row."""
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_exchange_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        assert isinstance(ret[r], tuple), ret[r]
+        assert ret[r][0] < 1e-5 and ret[r][1] == 3
+
+
 def _worker(rank, world, port, fail_rank, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
