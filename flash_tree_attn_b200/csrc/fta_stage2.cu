@@ -270,9 +270,11 @@ __global__ void __launch_bounds__(kThreads) exchange_scatter_kernel(const FtaExc
         }
     }
   }
-  __threadfence_system();
+  // One system-scope fence per block, after the barrier that makes the block's stores visible to
+  // thread 0 (a fence in every warp costs an NVLink round trip each and they queue up per SM).
   __syncthreads();
   if (t == 0) {
+    __threadfence_system();
     s_last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
     __threadfence();
   }
