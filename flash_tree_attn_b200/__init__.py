@@ -6,6 +6,7 @@ The arithmetic lives in libfta.so (hand-written sm_100a CUDA behind the C ABI of
 include/fta.h); build it with `python -m flash_tree_attn_b200.build`.
 """
 from .op import (  # noqa: F401
+    check_status,
     commit_accepted,
     flash_decoding_attention,
     flash_decoding_attention_paged,
@@ -17,7 +18,13 @@ from .op import (  # noqa: F401
     set_split_mode,
 )
 
+from .speculative import DraftTree, TreeVerifyAttention, accept_longest_path  # noqa: F401,E402
+
 __all__ = [
+    "check_status",
+    "DraftTree",
+    "TreeVerifyAttention",
+    "accept_longest_path",
     "commit_accepted",
     "flash_decoding_attention",
     "flash_decoding_attention_paged",

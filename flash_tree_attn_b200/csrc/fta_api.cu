@@ -89,6 +89,18 @@ int validate(const FtaParams* p) {
   return FTA_OK;
 }
 
+// The subset of validate() that the sizing entry points need before make_geom may index its
+// tables: sizes, head_dim and dtype (no pointers are read there).
+int validate_sizes(const FtaParams* p) {
+  if (!p) return FTA_E_BADARG;
+  if (p->B <= 0 || p->H <= 0 || p->Hkv <= 0 || p->Q <= 0 || p->ctx < 0) return FTA_E_BADARG;
+  if (p->B > FTA_MAX_BATCH) return FTA_E_UNSUPPORTED;
+  if (p->H % p->Hkv != 0) return FTA_E_BADARG;
+  if (p->D != 32 && p->D != 64 && p->D != 128 && p->D != 256) return FTA_E_BADARG;
+  if (p->dtype != FTA_DTYPE_F16 && p->dtype != FTA_DTYPE_BF16) return FTA_E_BADARG;
+  return FTA_OK;
+}
+
 struct DevInfo {
   int sms = 0;
 };
@@ -208,7 +220,7 @@ const char* fta_strerror(int code) {
 const char* fta_last_cuda_error(void) { return g_cuda_err; }
 
 int64_t fta_workspace_bytes(const FtaParams* p) {
-  if (!p) return -FTA_E_BADARG;
+  if (int rc = validate_sizes(p)) return -rc;
   FtaParams q = *p;
   q.split_mode = FTA_SPLIT_BALANCED;
   FtaGeom g;
@@ -218,7 +230,7 @@ int64_t fta_workspace_bytes(const FtaParams* p) {
 }
 
 int fta_plan_grid(const FtaParams* p) {
-  if (!p) return -FTA_E_BADARG;
+  if (int rc = validate_sizes(p)) return -rc;
   FtaGeom g;
   int rc = make_geom(*p, g, true);
   return rc ? -rc : g.grid;
@@ -332,8 +344,8 @@ int fta_commit_accepted(const FtaCommitParams* p, void* stream) {
 
 int64_t fta_plan_host(const FtaParams* p, const int64_t* lens, int64_t* segs_out, int64_t max_segs,
                       int32_t* grid_out, int32_t* per_out) {
-  if (!p || !lens) return -FTA_E_BADARG;
-  if (p->B <= 0 || p->B > FTA_MAX_BATCH || p->Hkv <= 0 || p->H % p->Hkv != 0 || p->Q <= 0) return -FTA_E_BADARG;
+  if (!lens) return -FTA_E_BADARG;
+  if (int rc = validate_sizes(p)) return -rc;
   FtaParams q = *p;
   q.split_mode = FTA_SPLIT_BALANCED;
   FtaGeom g;

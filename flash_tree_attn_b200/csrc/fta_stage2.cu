@@ -169,7 +169,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
-// Threads 1..world of the block (one per peer): tell the peer (when `signal`) and wait until the
+// Threads 0..world-1 of the block except this rank's own (one per peer): tell the peer (when `signal`) and wait until the
 // peer has told us; `slot` selects the first or the second flag round.  Returns through *fail a
 // bit per peer whose signal did not come within the limit.
 __device__ __forceinline__ void exchange_round(const FtaExchangeParams& p, int slot, bool signal, int* fail) {
@@ -241,7 +241,9 @@ __global__ void __launch_bounds__(kThreads) exchange_merge_kernel(const FtaExcha
 // its stores, "my slice is in your result buffer"; the kernel ends when every peer's slice is in.
 //   * Nobody stores into a peer's result buffer before that peer has signalled the first round of
 //     this call, i.e. before the peer's stream has passed everything that read the previous result.
-//   * p.done counts finished blocks and is set back to zero by the last one.
+//   * p.done[0] counts finished blocks and p.done[1] collects the waits that ran out in THIS launch;
+//     the last block sets both back to zero.  The second round is skipped when this launch lost a
+//     wait, whatever an earlier launch left in *p.status (which stays set until the host reads it).
 __global__ void __launch_bounds__(kThreads) exchange_scatter_kernel(const FtaExchangeParams p) {
   __shared__ int s_fail, s_last;
   const int t = threadIdx.x;
@@ -250,7 +252,10 @@ __global__ void __launch_bounds__(kThreads) exchange_scatter_kernel(const FtaExc
   exchange_round(p, 0, blockIdx.x == 0, &s_fail);
   __syncthreads();
   if (s_fail) {
-    if (t == 0) atomicOr(p.status, s_fail);
+    if (t == 0) {
+      atomicOr(p.status, s_fail);
+      atomicOr(p.done + 1, s_fail);
+    }
   } else {
     const int D4 = p.D >> 2;
     const int per = (p.rows + p.world - 1) / p.world;
@@ -281,8 +286,9 @@ __global__ void __launch_bounds__(kThreads) exchange_scatter_kernel(const FtaExc
   __syncthreads();
   if (!s_last) return;
   if (t == 0) {
-    *p.done = 0;
-    s_fail = *reinterpret_cast<volatile int*>(p.status);  // some block of this launch gave up: no second round
+    s_fail = *reinterpret_cast<volatile int*>(p.done + 1);  // some block of this launch gave up: no second round
+    p.done[0] = 0;
+    p.done[1] = 0;
   }
   __syncthreads();
   if (s_fail) return;

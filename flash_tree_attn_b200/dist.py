@@ -134,12 +134,15 @@ class PeerExchange:
         self.device = torch.device(device)
         self.timeout_ns = int(timeout_s * 1e9)
         self.epoch = 0
-        self._words = torch.zeros(2, dtype=torch.int32, device=self.device)  # status, finished-block count
+        self._words = torch.zeros(3, dtype=torch.int32, device=self.device)  # status; finished blocks, waits lost in the launch
         self.status = self._words[:1]
         self._keep = []
         self._params = None
         # plain peer mappings only: no NVLink multicast object is bound to this memory
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        if os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1") != "1":
+            raise RuntimeError("PeerExchange needs TORCH_SYMM_MEM_DISABLE_MULTICAST=1: its buffers must be plain peer "
+                               "mappings, never bound to an NVLink multicast object")
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
         self.local = symm_mem.empty(self.layout.total, dtype=torch.float32, device=self.device)
         self.local.zero_()
         hdl = symm_mem.rendezvous(self.local, self.group)

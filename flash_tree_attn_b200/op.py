@@ -27,7 +27,6 @@ _kernel = {"auto": _lib.KERNEL_AUTO, "mma": _lib.KERNEL_MMA, "umma": _lib.KERNEL
 _grid_override = int(os.environ.get("FTA_GRID", "0"))
 
 _scratch = {}  # (device index, stream, tag) -> tensor, grown on demand
-_ws_bytes_cache = {}
 
 
 def set_split_mode(mode: str) -> None:
@@ -59,6 +58,23 @@ def _scratch_buf(dev: torch.device, stream: int, tag: str, nbytes: int) -> torch
     return t
 
 
+_warned_cache_copy = False
+
+
+def _warn_cache_copy(t: torch.Tensor) -> None:
+    global _warned_cache_copy
+    if not _warned_cache_copy:
+        import warnings
+
+        _warned_cache_copy = True
+        warnings.warn(
+            f"flash_decoding_attention: KV cache with strides {tuple(t.stride())} / data pointer alignment "
+            f"{t.data_ptr() % 16} is copied to a contiguous layout on every call "
+            f"({2 * t.numel() * t.element_size() / 2**20:.0f} MiB per call); give the caches unit stride in head_dim, "
+            "other strides that are multiples of 8 elements and a 16-byte aligned base to avoid it", RuntimeWarning,
+            stacklevel=4)
+
+
 def _rows_ok(t: torch.Tensor) -> bool:
     if t.stride(-1) != 1 or t.data_ptr() % 16:
         return False
@@ -68,17 +84,24 @@ def _rows_ok(t: torch.Tensor) -> bool:
 def _mask_strides(mask: torch.Tensor, B: int, H: int, Q: int):
     """fp32 additive mask -> (tensor, stride_b, stride_h, stride_q); 0 broadcasts.
 
-    Accepted shapes: [Q,Q], [B,Q,Q], [B,1,Q,Q], [B,H,Q,Q] (and size-1 broadcast dims), the
-    set that broadcasts against the reference's [B,H,Q,Q] scores (flash_tree_attn.py:368)
-    plus the 3-D per-sequence form.
+    Accepted shapes: [Q,Q], [H,Q,Q], [B,1,Q,Q], [B,H,Q,Q] (and size-1 broadcast dims), the
+    set that broadcasts against the reference's [B,H,Q,Q] scores (flash_tree_attn.py:368),
+    plus [B,Q,Q] read per sequence when B != H.
     """
     if mask.dtype != torch.float32 or mask.stride(-1) != 1:
         mask = mask.float().contiguous()
     if mask.dim() == 2:
         sb = sh = 0
     elif mask.dim() == 3:
-        sb, sh = (mask.stride(0) if mask.size(0) > 1 else 0), 0
-        assert mask.size(0) in (1, B), "mask batch dimension does not match q"
+        # The reference adds the mask to [B,H,Q,Q] scores, so torch broadcasting reads a 3-D mask's
+        # first dimension as HEADS (flash_tree_attn.py:368).  That reading is kept whenever the size
+        # fits it (also when bsz == num_heads); a first dimension of bsz != num_heads, which the
+        # reference rejects, is read per sequence.  Pass [bsz,1,Q,Q] to be explicit.
+        if mask.size(0) == H and H > 1:
+            sb, sh = 0, mask.stride(0)
+        else:
+            sb, sh = (mask.stride(0) if mask.size(0) > 1 else 0), 0
+            assert mask.size(0) in (1, B), "mask's first dimension matches neither num_heads nor bsz"
     elif mask.dim() == 4:
         sb = mask.stride(0) if mask.size(0) > 1 else 0
         sh = mask.stride(1) if mask.size(1) > 1 else 0
@@ -169,10 +192,11 @@ def prepare(
 
     if not _rows_ok(q):
         q = q.contiguous()
-    if not _rows_ok(k_cache):
-        k_cache = k_cache.contiguous()
-    if not _rows_ok(v_cache):
-        v_cache = v_cache.contiguous()
+    if not (_rows_ok(k_cache) and _rows_ok(v_cache)):
+        # every copy engine here moves 16-byte row chunks; a cache laid out otherwise has to be
+        # re-packed, which costs a full read and write of it on every call: say so, once
+        _warn_cache_copy(k_cache)
+        k_cache, v_cache = k_cache.contiguous(), v_cache.contiguous()
     if kv_seq_len.dtype not in (torch.int32, torch.int64) or not kv_seq_len.is_contiguous():
         kv_seq_len = kv_seq_len.to(torch.int64).contiguous()
     if kv_seq_len.device != dev:
@@ -239,13 +263,11 @@ def prepare(
     if output is None and not block_mode:
         # planner-balanced splits, fixed-size workspace
         p.split_mode = _lib.SPLIT_BALANCED
-        key = (dev.index, B, H, Hkv, Q, D, p.dtype, _kernel, _grid_override)
-        nbytes = _ws_bytes_cache.get(key)
-        if nbytes is None:
-            nbytes = lib.fta_workspace_bytes(C.byref(p))
-            if nbytes < 0:
-                raise _lib.FtaError(-nbytes, "fta_workspace_bytes")
-            _ws_bytes_cache[key] = nbytes
+        # asked every time: the size depends on the kernel family the library picks for THESE
+        # strides and options, and the query is a few hundred nanoseconds of host arithmetic
+        nbytes = lib.fta_workspace_bytes(C.byref(p))
+        if nbytes < 0:
+            raise _lib.FtaError(-nbytes, "fta_workspace_bytes")
         ws = _scratch_buf(dev, stream, "ws", nbytes)
         p.workspace = ws.data_ptr(); p.workspace_bytes = ws.numel()
         keep.append(ws)
@@ -460,6 +482,20 @@ def commit_accepted(k_cache, v_cache, current_k, current_v, kv_seq_len, accept_i
     # the temporaries above are read by the kernels after this returns: tie them to the stream
     for t in keep:
         t.record_stream(torch.cuda.current_stream(dev))
+
+
+def check_status() -> None:
+    """Synchronise the current device and raise if a kernel of the tcgen05 stage-1 family gave up on
+    one of its bounded barrier waits since the last check (a protocol error: the block then leaves
+    early and the call's output is not a result).  The status is sticky until read here.  The
+    operator itself never synchronises, so a caller that wants this certainty calls it at a point
+    where a synchronisation is acceptable, e.g. once per decoded token batch or at shutdown."""
+    st = _lib.load().fta_umma_status()
+    if st < 0:
+        raise RuntimeError("fta_umma_status: the status word could not be read")
+    if st:
+        raise RuntimeError(f"tcgen05 stage-1 kernel: a bounded barrier wait ran out (site code {st:#x}); "
+                           "outputs of calls since the last check are not results")
 
 
 def merge_partials(part_o: torch.Tensor, part_lse: torch.Tensor, out_dtype: torch.dtype = torch.float32):

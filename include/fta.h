@@ -167,7 +167,8 @@ typedef struct FtaMergeParams {
  *                 elements [world, 2 * world) serve the second round of the scatter form
  *   epoch         1, 2, 3, ... (mod 2^32) the same on every rank for the same call
  *   status        device word; bit s is set when the wait for rank s ran out (bit 8 + s: in the
- *                 second round); what was stored by then is not a result
+ *                 second round); what was stored by then is not a result.  The word is
+ *                 sticky: the kernels only ever set bits, the host clears it after reading
  *   timeout_ns    bound of each wait
  * Two forms.
  *   done == NULL ("gather"): every rank reads every peer's whole partial and writes all rows of
@@ -175,8 +176,9 @@ typedef struct FtaMergeParams {
  *   done != NULL ("scatter"): rank r merges rows [r * ceil(rows / world), ...) only and stores
  *     them into EVERY rank's result through out_peer[s] / lse_peer[s] (rank s's result buffers as
  *     mapped here; entry [rank] is this rank's own; out and lse are not used); a second flag
- *     round tells the peers that the slice has arrived.  `done` is a zeroed device int32 private
- *     to the rank.  Less NVLink traffic with many ranks: one partial in and half a result out per
+ *     round tells the peers that the slice has arrived.  `done` points at two zeroed device
+ *     int32s private to the rank (finished blocks; waits lost in the current launch), which the
+ *     kernel leaves at zero.  Less NVLink traffic with many ranks: one partial in and half a result out per
  *     GPU instead of (world - 1) partials in.
  * The caller alternates between two partial buffers from call to call (a peer may still read the
  * previous one) and makes the calls in the same order on every rank.  One result buffer per rank

@@ -23,6 +23,10 @@ def _mask_for(mask: torch.Tensor, b: int, H: int, Q: int) -> torch.Tensor:
     if m.dim() == 2:
         return m[None]
     if m.dim() == 3:
+        # torch broadcasting against [B,H,Q,Q] scores (flash_tree_attn.py:368) reads the first
+        # dimension as heads; a first dimension that is not num_heads is read per sequence
+        if m.size(0) == H and H > 1:
+            return m
         return m[b if m.size(0) > 1 else 0][None]
     mb = m[b if m.size(0) > 1 else 0]
     return mb  # [H or 1, Q, Q]

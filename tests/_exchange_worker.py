@@ -4,7 +4,8 @@ Every rank owns a contiguous KV range of one long sequence.  The same call goes 
 path (all-gather of the packed partials, then fta_merge_parts) and through fta_exchange_merge over
 peer-mapped memory; both fold the ranks' partials in rank order with the same arithmetic, so the
 results must be identical bit for bit, many calls in a row (two alternating buffers, growing
-epochs).  Both forms of the exchange are run.  Prints one line "EXCHANGE_OK <form> ..." per rank and form
+epochs).  Both forms of the exchange are run, and the
+result is also held against the fp32 oracle of the whole sequence.  Prints one line "EXCHANGE_OK <form> ..." per rank and form
 on success.
 """
 import os
@@ -59,6 +60,15 @@ def one_form(form, fdist, dist, inp, w, k_sh, v_sh, shard_len, dev, rank, world,
         assert torch.equal(l_ref, l_x), f"rank {rank}: LSEs differ"
         worst = max(worst, float(o_x.float().abs().max()))
     assert worst > 0.0 and torch.isfinite(o_x.float()).all()
+
+    # and against the fp32 oracle of the WHOLE sequence (every rank holds all of it here)
+    from oracle.tree_attention_oracle import tree_attention_oracle
+
+    ora = tree_attention_oracle(q, inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"], inp["mask"],
+                                inp["kv_seq_len"], None, w.G)
+    eo = float((o_x.float() - ora["out"]).abs().max())
+    el = float((l_x - ora["lse"]).abs().max())
+    assert eo <= 2e-3 + 2.0 ** -8 * float(ora["out"].abs().max()) and el <= 1e-3, f"rank {rank}: {form}: out {eo} lse {el} off the oracle"
 
     # the prepared form gives the same bits, run after run, interleaved with plain calls
     prep = fdist.PreparedKvRange(inp["q"], k_sh, v_sh, inp["current_k"], inp["current_v"], inp["mask"], shard_len,

@@ -85,6 +85,21 @@ def test_decode_rejects_bad_arguments(fta_lib):
     assert fta_lib.fta_decode(None, None) == _lib.FTA_E_BADARG
 
 
+def test_sizing_entry_points_validate_sizes_and_dtype(fta_lib):
+    """fta_workspace_bytes / fta_plan_grid / fta_plan_host read sizes only, but they index tables by
+    dtype and head_dim: bad values must come back as an error code, not as an out-of-range read."""
+    good = _params(2, 8, 8, 8, 64, 128, 4)
+    assert fta_lib.fta_workspace_bytes(C.byref(good)) > 0 and fta_lib.fta_plan_grid(C.byref(good)) == 4
+    lens = (C.c_int64 * 2)(100, 37)
+    for field, value in (("dtype", 7), ("dtype", -1), ("D", 48), ("Hkv", 3), ("B", 0), ("Q", 0)):
+        p = _params(2, 8, 8, 8, 64, 128, 4)
+        setattr(p, field, value)
+        assert fta_lib.fta_workspace_bytes(C.byref(p)) == -_lib.FTA_E_BADARG, field
+        assert fta_lib.fta_plan_grid(C.byref(p)) == -_lib.FTA_E_BADARG, field
+        assert fta_lib.fta_plan_host(C.byref(p), lens, None, 0, None, None) == -_lib.FTA_E_BADARG, field
+    assert fta_lib.fta_workspace_bytes(None) == -_lib.FTA_E_BADARG
+
+
 def test_paged_cache_arguments_are_validated(fta_lib):
     """Pointers here are fake but aligned: validation ends before anything is dereferenced or
     launched.  A page must hold whole 64-row tiles and the table must cover ctx."""

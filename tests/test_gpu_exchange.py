@@ -45,17 +45,35 @@ class _Emulated:
             l[s::7] = float("-inf")  # empty partial rows contribute nothing
             self.bufs.append(torch.cat([o.reshape(-1), l]))
         self.flags = torch.zeros(2, 4, dtype=torch.int32, device="cuda")   # [rank][round * world + from]
-        self.words = torch.zeros(2, 2, dtype=torch.int32, device="cuda")   # [rank][status, finished blocks]
+        self.words = torch.zeros(2, 3, dtype=torch.int32, device="cuda")   # [rank][status, finished blocks, waits lost in the launch]
         self.out = torch.full((2, rows, D), float("nan"), device="cuda")
         self.lse = torch.full((2, rows), float("nan"), device="cuda")
 
     def want(self):
+        """What the merge must give: the oracle's closed form (fp32, to rounding), and, bit for
+        bit, the library's own merge of gathered partials (the NCCL path folds the ranks' partials
+        in the same order with the same arithmetic)."""
         import flash_tree_attn_b200 as fta
+        from oracle.tree_attention_oracle import merge_partials_oracle
 
         n = self.rows * self.D
         po = torch.stack([b[:n].view(self.rows, self.D) for b in self.bufs])
         pl = torch.stack([b[n:] for b in self.bufs])
-        return fta.merge_partials(po, pl, torch.float32)
+        o, l = fta.merge_partials(po, pl, torch.float32)
+        oo, ol = merge_partials_oracle(po, pl)
+        # rows whose partials are all empty have no LSE to compare (-inf on both sides)
+        fin = torch.isfinite(ol)
+        assert torch.equal(torch.isfinite(l), fin)
+        assert (o - oo).abs().max().item() <= 1e-5 and (l[fin] - ol[fin]).abs().max().item() <= 1e-5
+        self.oracle = (oo, ol)
+        return o, l
+
+    def check_oracle(self, out, lse, rows=slice(None)):
+        """fp32 results of the exchange kernels against the oracle's merge."""
+        oo, ol = self.oracle
+        fin = torch.isfinite(ol[rows])
+        assert (out[rows] - oo[rows]).abs().max().item() <= 1e-5
+        assert (lse[rows][fin] - ol[rows][fin]).abs().max().item() <= 1e-5
 
     def launch(self, rank, epoch, scatter, timeout_ns=200_000_000):
         import ctypes as C
@@ -98,6 +116,7 @@ def test_gather_form_on_one_gpu_and_its_timeout():
     assert e.launch(0, 5, scatter=False) == 0
     assert int(e.flags[1, 0].item()) == 5  # rank 0's signal in rank 1's array
     assert torch.equal(e.out[0], want_o) and torch.equal(e.lse[0], want_l)
+    e.check_oracle(e.out[0], e.lse[0])
 
     e.out.fill_(float("nan"))
     assert e.launch(0, 6, scatter=False, timeout_ns=50_000_000) == 0b10  # rank 1 never signals call 6
@@ -129,6 +148,7 @@ def test_scatter_form_on_one_gpu_and_its_timeouts():
     assert e.launch(1, 9, scatter=True) == 0
     for s in range(2):
         assert torch.equal(e.out[s], want_o) and torch.equal(e.lse[s], want_l)
+        e.check_oracle(e.out[s], e.lse[s])
 
     # first round runs out: nothing stored, counter reset, no second-round signal
     e.out.fill_(float("nan"))
@@ -144,3 +164,11 @@ def test_scatter_form_on_one_gpu_and_its_timeouts():
     e.words.zero_()
     e.flags[0, 3] = 10
     assert e.launch(0, 10, scatter=True) == 0
+    # a status word the host has not read yet (an old timeout) is sticky, but it must not make
+    # later calls skip their second round: the peers would then wait out their limit on every call
+    e.words[0, 0] = 0b10
+    e.flags[0, 1] = e.flags[0, 3] = 11
+    e.flags[1, 2] = 0
+    assert e.launch(0, 11, scatter=True) == 0b10
+    assert int(e.flags[1, 2].item()) == 11
+    assert int(e.words[0, 1].item()) == 0 and int(e.words[0, 2].item()) == 0

@@ -219,7 +219,7 @@ def test_int64_lengths_and_strided_views(fta):
     _check(out, lse, _oracle(inp, 1), "strided")
 
 
-@pytest.mark.parametrize("mask_kind", ["2d", "3d", "4d_b1", "4d_bh", "ones"])
+@pytest.mark.parametrize("mask_kind", ["2d", "3d", "3d_heads", "4d_b1", "4d_bh", "ones"])
 def test_mask_forms(fta, mask_kind):
     """Additive mask semantics: any finite allowed value is added (the reference's test uses
     1.0, flash_tree_attn.py:409), and every broadcastable shape is accepted."""
@@ -230,6 +230,8 @@ def test_mask_forms(fta, mask_kind):
     m = ancestor_mask(tree_parents("random", 16, 3), 1.0 if mask_kind == "ones" else 0.0).cuda()
     if mask_kind == "3d":
         m = torch.stack([m, ancestor_mask(tree_parents("random", 16, 4)).cuda()])
+    elif mask_kind == "3d_heads":  # [num_heads, Q, Q]: torch broadcasting against [B,H,Q,Q], as in the reference
+        m = torch.stack([ancestor_mask(tree_parents("random", 16, 20 + h)).cuda() for h in range(4)])
     elif mask_kind == "4d_b1":
         m = torch.stack([m, ancestor_mask(tree_parents("random", 16, 5)).cuda()])[:, None]
     elif mask_kind == "4d_bh":
@@ -334,6 +336,53 @@ def test_benchmark_shapes(fta, cfg, B, kernel):
     inp = make_inputs(w, "cuda")
     out, lse = _run(fta, inp, w.G, ctx=w.ctx)
     _check(out, lse, _oracle(inp, w.G), cfg)
+
+
+@pytest.mark.parametrize("cfg", ["cfg3", "cfg4", "cfg5"])
+def test_benchmark_shapes_at_full_size(fta, cfg):
+    """The configurations the benchmark times, whole (32 sequences of cfg3, all 131072 rows of cfg4,
+    the 128 ragged sequences of cfg5; cfg2 runs whole in test_benchmark_shapes): at full size the
+    balanced plan has other tile ranges per block, 64-bit line positions where the line is long,
+    more pieces per unit and a wrapped descriptor ring, which is what the timed launches exercise."""
+    from flash_tree_attn_b200.workloads import WORKLOADS, make_inputs
+
+    fta.set_kernel("auto")
+    w = WORKLOADS[cfg]
+    inp = make_inputs(w, "cuda")
+    out, lse = _run(fta, inp, w.G, ctx=w.ctx)
+    _check(out, lse, _oracle(inp, w.G), cfg + " full size")
+    del inp
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_reference_test_case_at_its_own_size(fta, kernel):
+    """The reference's only test, test_tree_op (flash_tree_attn.py:416-440), at its own size and
+    conventions: Z=32, H=32, N_CTX=4096, head_dim 128, q_len 128, block_size 128 passed
+    positionally, int64 lengths all equal to N_CTX, q/k/v ~ N(0, 0.5), tree tokens ~ N(0, 1), a random
+    0/1 visibility pattern with the diagonal set whose allowed entries are 1.0 (added to the scores),
+    fp16.  The reference accepts atol 1e-2 against its dense torch evaluation; here 2e-3 against
+    the fp32 oracle, which follows that evaluation."""
+    fta.set_kernel(kernel)
+    Z, H, N_CTX, D, q_len = 32, 32, 4096, 128, 128
+    g = torch.Generator(device="cuda").manual_seed(416)
+    rnd = lambda shape, std: (torch.randn(shape, generator=g, device="cuda") * std).half()
+    inp = {"q": rnd((Z, H, q_len, D), 0.5), "k_cache": rnd((Z, H, N_CTX, D), 0.5), "v_cache": rnd((Z, H, N_CTX, D), 0.5),
+           "current_k": rnd((Z, H, q_len, D), 1.0), "current_v": rnd((Z, H, q_len, D), 1.0)}
+    vis = torch.rand((q_len, q_len), generator=g, device="cuda") < 0.5
+    vis |= torch.eye(q_len, dtype=torch.bool, device="cuda")
+    inp["mask"] = torch.where(vis, 1.0, float("-inf")).float()
+    inp["kv_seq_len"] = torch.tensor([N_CTX] * Z).cuda()  # int64, as the reference's test builds it
+    assert inp["kv_seq_len"].dtype == torch.int64
+    out = fta.flash_decoding_attention(inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"],
+                                       inp["mask"], inp["kv_seq_len"], 128)
+    out2, lse = _run(fta, inp, 1, 128)
+    assert torch.equal(out, out2)
+    ora = _oracle(inp, 1)
+    _check(out, lse, ora, "reference test case")
+    assert torch.allclose(ora["out"], out.float(), atol=1e-2, rtol=0)  # the reference's own criterion
+    del inp
+    torch.cuda.empty_cache()
 
 
 def test_kv_range_shards_merge_to_whole(fta):

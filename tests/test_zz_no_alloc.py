@@ -5,8 +5,9 @@ runtime that has claimed the whole device heap, or as a plugin that must leave i
 allocator alone.  For them the library carries its own fixed scratch array.  This test calls
 that entry point through the C ABI, twice in a row (the array is shared between calls and
 keeps the previous call's contents), and checks each result against what the ordinary entry
-point returns for the same inputs, to the tolerance the parity tests use.  The file sorts last
-so that a run that stops at the first failure has already run every other test.
+point returns for the same inputs and against the fp32 oracle, to the tolerance the parity tests
+use; it also checks that the device's free memory is the same after the call as before it.  The
+file sorts last so that a run that stops at the first failure has already run every other test.
 """
 import ctypes as C
 
@@ -31,6 +32,7 @@ def test_static_scratch_entry_point_matches_regular_one(kernel):
     assert torch.cuda.is_available()
     import flash_tree_attn_b200 as fta
     from flash_tree_attn_b200 import _lib
+    from oracle.tree_attention_oracle import tree_attention_oracle
 
     lib = _lib.load()
     assert lib.fta_static_scratch_bytes() == 24 << 20
@@ -50,13 +52,30 @@ def test_static_scratch_entry_point_matches_regular_one(kernel):
             call.lse.fill_(float("nan"))
             call.p.workspace = None
             call.p.workspace_bytes = 0
+            # The first call on a device is the documented set-up call (it resolves the address of the
+            # library's scratch array, which is when the CUDA runtime loads that part of the library
+            # image onto the device); what is measured is a call after it.
+            assert lib.fta_decode_static(C.byref(call.p), call.stream) == 0
+            torch.cuda.synchronize()
+            call.out.fill_(float("nan"))
+            call.lse.fill_(float("nan"))
+            torch.cuda.synchronize()
+            # nothing may be taken from the device heap: neither through torch's allocator nor
+            # behind its back (cudaMemGetInfo sees every allocation of the process)
+            torch_before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
             rc = lib.fta_decode_static(C.byref(call.p), call.stream)
             assert rc == 0, lib.fta_strerror(rc)
             torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated() == torch_before
+            assert torch.cuda.mem_get_info()[0] == free_before
             assert lib.fta_umma_status() == 0
             assert torch.isfinite(call.out.float()).all()
             assert (call.out.float() - ref_out.float()).abs().max().item() <= OUT_TOL
             assert (call.lse - ref_lse).abs().max().item() <= LSE_TOL
+            ora = tree_attention_oracle(inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"],
+                                        inp["mask"], inp["kv_seq_len"], None, w.G)
+            assert (call.out.float() - ora["out"]).abs().max().item() <= OUT_TOL
+            assert (call.lse - ora["lse"]).abs().max().item() <= LSE_TOL
     finally:
         fta.set_kernel("auto")
 
