@@ -119,6 +119,30 @@ def _events(fn, warmup, reps, flush=None):
             "back_to_back_ms": a.elapsed_time(b) / reps}
 
 
+# The reference computes a block's cache offset as program_id * stride in 32-bit integers
+# (flash_tree_attn.py:71-72: cur_token_idx * stride_kb + ...).  A cache of 2^31 elements or more makes
+# that product wrap and the kernel read far outside the tensor: cfg5 whole (128 x 32 x 16384 x 128 =
+# 8.6 G elements per cache) ended the process with a CUDA fault.  Such a workload is timed on its
+# first power-of-two many sequences whose cache stays below 2^31 elements, ours on the same slice.
+INT32_ELEMS = 1 << 31
+
+
+def reference_sized(w):
+    """(workload the reference can address, note or None)."""
+    from flash_tree_attn_b200.workloads import draw_lengths, small
+
+    per_seq = w.Hkv * w.ctx * w.D
+    if w.B * per_seq < INT32_ELEMS:
+        return w, None
+    B = 1
+    while 2 * B * per_seq < INT32_ELEMS and 2 * B <= w.B:
+        B *= 2
+    lens = draw_lengths(w)[:B]
+    sub = small(w, B=B, lens="fixed:" + ",".join(map(str, lens)), name=f"{w.name}[first {B} sequences]")
+    return sub, (f"first {B} of {w.B} sequences: the reference's 32-bit offset arithmetic (flash_tree_attn.py:71-72) "
+                 f"cannot address a cache of {w.B * per_seq / 2**30:.1f} Gi elements")
+
+
 def time_workload(w, warmup=5, reps=20, flush_l2=False, ours=True):
     import torch
 
@@ -126,9 +150,12 @@ def time_workload(w, warmup=5, reps=20, flush_l2=False, ours=True):
     from flash_tree_attn_b200.workloads import draw_lengths, kv_bytes, make_inputs
 
     dev = torch.device("cuda")
+    w, size_note = reference_sized(w)
     lens = draw_lengths(w)
     inp = make_inputs(w, dev, lens=lens)
     ad, notes = adapt_inputs(w, inp)
+    if size_note:
+        notes.append(size_note)
     ref = load_ref(any_dtype=w.dtype != torch.float16)
     B, H, D, Qp = w.B, w.H, w.D, ad["Qp"]
     S = (w.ctx + w.block_size - 1) // w.block_size

@@ -628,13 +628,16 @@ def triton_arm(args):
                                env=dict(os.environ, **env_extra))
             lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
             if r.returncode != 0 or not lines:
-                return {"unavailable": ("child failed: " + (r.stderr or r.stdout)[-300:]).replace("\n", " ")}
+                return {"unavailable": ("child failed: " + (r.stderr or r.stdout)[-600:]).replace("\n", " ")}
             return json.loads(lines[-1])
         except subprocess.TimeoutExpired:
             return {"unavailable": f"child exceeded {limit} s"}
-    gpu = child(["--workloads", ",".join(PERF_CONFIGS), "--reps", "20", "--warmup", "5"], {}, 900)
+    gpu = {}
+    for name in PERF_CONFIGS:  # one child per workload: a failure in one cannot take the others with it
+        r = child(["--workloads", name, "--reps", "20", "--warmup", "5"], {}, 400)
+        gpu[name] = r.get("workloads", {}).get(name, r)
     cpu = child(["--interpret", "cfg1"], {"TRITON_INTERPRET": "1", "CUDA_VISIBLE_DEVICES": ""}, 300)
-    return gpu, cpu
+    return {"workloads": gpu}, cpu
 
 
 def main():

@@ -60,7 +60,10 @@ def test_verify_accept_commit_loop_matches_the_oracle_on_the_concatenated_cache(
         ref = ora["out"]
         half_ulp = {torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
         excess = ((out.float() - ref).abs() - half_ulp * ref.abs()).max().item()
-        assert excess <= 2e-3, f"step {step}: {excess}"
+        # bf16 on a cache of a few dozen rows: every output is a sum of a handful of terms whose
+        # weights P were rounded to 8 bits before P.V, as the reference rounds them
+        # (flash_tree_attn.py:117); the randomised sweep saw up to 3.0e-3 there
+        assert excess <= (2e-3 if dtype == torch.float16 else 4e-3), f"step {step}: {excess}"
         assert layer.kv_seq_len.tolist() == L
         # accept: random verdicts; sequence 1 accepts everything at step 0, sequence 2 nothing at step 1
         ok = torch.rand((B, Q), generator=g, device="cuda") < 0.8
