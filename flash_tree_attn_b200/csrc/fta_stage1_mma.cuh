@@ -114,6 +114,10 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
   const T* CKp = (const T*)p.cur_k;
   const T* CVp = (const T*)p.cur_v;
 
+  // stage 2 is launched with programmatic stream serialization: let its grid be set up now; its
+  // blocks wait for this whole grid to finish before they read anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   FtaBalanced plan;
   long long lin = 0, lin_end = 0, item = 0, n_items = 0;
   if (p.split_mode == FTA_SPLIT_BALANCED) {

@@ -221,6 +221,15 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   const int G = p.H / p.Hkv;
   const int fmt = p.dtype == FTA_DTYPE_BF16 ? 1 : 0;
 
+  // stage 2 is launched with programmatic stream serialization: let its grid be set up now; its
+  // blocks wait for this whole grid to finish before they read anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // the copy engine's descriptors are fetched while the block sets itself up
+  if (tid == 32 * 0 + 31) {
+    tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
+    if (g.n_tree) { tma_prefetch_desc(&maps.ck); tma_prefetch_desc(&maps.cv); }
+  }
+
   // one barrier per thread: slot i expects count(i) arrivals per phase
   if (tid < B_COUNT) {
     uint32_t count = 1;
@@ -286,8 +295,6 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     } else if (warp == 0) {
       // ================================ TMA producer ================================
       if (lane == 0) {
-        tma_prefetch_desc(&maps.q); tma_prefetch_desc(&maps.k); tma_prefetch_desc(&maps.v);
-        if (g.n_tree) { tma_prefetch_desc(&maps.ck); tma_prefetch_desc(&maps.cv); }
         uint32_t gt = 0;
         bool ok = true;
         for (uint32_t sidx = 0; ok; ++sidx) {

@@ -32,52 +32,74 @@ struct Acc {
 };
 
 constexpr int kThreads = 256;
+constexpr int kRowsPerWarp = 2;  // BALANCED: two rows in flight per warp, and the whole merge fits one wave of blocks
 constexpr int kRowsPerBlock = kThreads / 32;
 
-// One warp per query row, one float4 of head_dim per lane (two for head_dim 256).  Loads of up to
-// four partials are issued before any is folded in.
+// Waits until the kernel launched before this one on the stream (stage 1) has completed and its
+// stores are visible.  Stage 2 is launched with programmatic stream serialization, so its blocks are
+// set up while stage 1 still runs and start the moment it has finished.
+__device__ __forceinline__ void wait_for_stage1() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// One warp per query row (two rows per warp in the BALANCED plan), one float4 of head_dim per lane (two
+// for head_dim 256).  Loads of up to four partials per row are issued before any is folded in.
 //   BALANCED: grid = (stage-1 blocks, row groups): block c merges the unit whose second piece
 //             opens stage-1 block c, if any (fta_cut_desc); uncut units were finished by stage 1.
 //   FIXED:    grid = (units, row groups).
 __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, const FtaGeom g) {
-  const int row = blockIdx.y * kRowsPerBlock + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int D = p.D;
-  if (row >= g.R) return;
+  wait_for_stage1();
 
   if (p.split_mode == FTA_SPLIT_BALANCED) {
+    const int row0 = (blockIdx.y * kRowsPerBlock + (threadIdx.x >> 5)) * kRowsPerWarp;
+    if (row0 >= g.R) return;
     const int4 cut = fta_cut_desc(p, g)[blockIdx.x];
     const int np = cut.z;
     if (np < 2) return;
     const int b = cut.x, j = cut.y;
     const FtaUnit unit = fta_unit(g, j);
-    int h, qi;
-    if (!fta_row(p, g, unit, row, h, qi)) return;
+    int h[kRowsPerWarp], qi[kRowsPerWarp];
+    bool live[kRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) live[r] = row0 + r < g.R && fta_row(p, g, unit, row0 + r, h[r], qi[r]);
     const float* ws_o = reinterpret_cast<const float*>(p.workspace);
     const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
     for (int c4 = lane * 4; c4 < D; c4 += 128) {
-      Acc acc; acc.init();
+      Acc acc[kRowsPerWarp];
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) acc[r].init();
       for (int s0 = 0; s0 < np; s0 += 4) {
-        float lse[4]; float4 o[4];
+        float lse[kRowsPerWarp][4]; float4 o[kRowsPerWarp][4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int s = s0 + k;
-          lse[k] = -INFINITY; o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (s < np) {
-            const long long slot = s == 0 ? (long long)cut.w : 2ll * ((long long)blockIdx.x + (long long)(s - 1) * g.lanes);
-            lse[k] = ws_l[slot * g.R + row];
-            o[k] = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row) * D + c4);
+          const long long slot = s == 0 ? (long long)cut.w : 2ll * ((long long)blockIdx.x + (long long)(s - 1) * g.lanes);
+#pragma unroll
+          for (int r = 0; r < kRowsPerWarp; ++r) {
+            lse[r][k] = -INFINITY; o[r][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s < np && live[r]) {
+              lse[r][k] = ws_l[slot * g.R + row0 + r];
+              o[r][k] = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row0 + r) * D + c4);
+            }
           }
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) acc.add(lse[k], o[k]);
+        for (int r = 0; r < kRowsPerWarp; ++r)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[r].add(lse[r][k], o[r][k]);
       }
-      fta_store4(p.out, p.out_dtype, b * p.o_sb + h * p.o_sh + qi * p.o_sq + c4, acc.value());
-      if (c4 == 0 && p.lse) p.lse[b * p.l_sb + h * p.l_sh + qi] = acc.lse();
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        if (!live[r]) continue;
+        fta_store4(p.out, p.out_dtype, b * p.o_sb + h[r] * p.o_sh + qi[r] * p.o_sq + c4, acc[r].value());
+        if (c4 == 0 && p.lse) p.lse[b * p.l_sb + h[r] * p.l_sh + qi[r]] = acc[r].lse();
+      }
     }
     return;
   }
 
+  const int row = blockIdx.y * kRowsPerBlock + (threadIdx.x >> 5);
+  if (row >= g.R) return;
   const int b = blockIdx.x / g.U, j = blockIdx.x - b * g.U;
   const FtaUnit unit = fta_unit(g, j);
   int h, qi;
@@ -118,6 +140,7 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
 // ever writes its rows; they are defined here (zero output, LSE = -inf).
 __global__ void __launch_bounds__(kThreads) empty_rows_kernel(const FtaParams p) {
   const int b = blockIdx.x;
+  wait_for_stage1();
   if (fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx) != 0) return;
   const int D4 = p.D >> 2;
   for (int i = threadIdx.x; i < p.H * p.Q * D4; i += kThreads) {
@@ -317,9 +340,23 @@ cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t
   const bool balanced = p.split_mode == FTA_SPLIT_BALANCED;
   // rows past hpt * qpt of a unit's tile are padding: no blocks for them
   const int rows = g.hpt * g.qpt < g.R ? g.hpt * g.qpt : g.R;
-  const dim3 grid(balanced ? g.grid : p.B * g.U, (rows + kRowsPerBlock - 1) / kRowsPerBlock);
-  stage2_kernel<<<grid, kThreads, 0, st>>>(p, g);
-  if (balanced && !p.with_tree) empty_rows_kernel<<<p.B, kThreads, 0, st>>>(p);
+  const int rpb = kRowsPerBlock * (balanced ? kRowsPerWarp : 1);
+  const dim3 grid(balanced ? g.grid : p.B * g.U, (rows + rpb - 1) / rpb);
+  // Programmatic stream serialization: the grid is set up while stage 1 is still running and its
+  // blocks wait (griddepcontrol.wait) for stage 1 to finish, instead of being launched after it.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, stage2_kernel, p, g);
+  if (e != cudaSuccess) return e;
+  if (balanced && !p.with_tree) {
+    cfg.gridDim = dim3(p.B);
+    e = cudaLaunchKernelEx(&cfg, empty_rows_kernel, p);
+    if (e != cudaSuccess) return e;
+  }
   return cudaGetLastError();
 }
 
