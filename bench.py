@@ -245,7 +245,8 @@ def workload_config(w, lens, world=1, extra=None):
         "sum_kv_len": int(sum(lens)),
         "parallelism": ("one GPU" if world == 1 else
                         (f"one job, KV range split over {world} GPUs" if (w.B == 1 and w.lens == "full") else
-                         f"one job, its {w.B} sequences dealt to {world} GPUs by KV length, no collective")),
+                         f"one job, its {w.B} sequences dealt to {world} GPUs by KV length" +
+                         (", KV heads split where sequences run out" if w.B < world else "") + ", no collective")),
         "l2": ("inputs larger than L2: the KV rows one call streams exceed the 126 MB L2, no flush needed"
                if 2 * 2 * w.D * (w.H // w.G) * sum(lens) / world > (126 << 20) else
                "inputs smaller than L2 and not flushed between iterations: a launch-latency figure, not a bandwidth one"),
@@ -389,11 +390,11 @@ class E2E:
         }
 
 
-def stage1_roofline(env, w, name, ms_stage1, my_lens, args):
+def stage1_roofline(env, w, name, ms_stage1, my_lens, args, head_share=1.0):
     """Roofline object of the stage-1 kernel, for the rank whose launch takes longest."""
     hbm_peak, tf_peak, tf_sust, peak_src = measured_peaks()
-    kvb = 2 * 2 * w.D * w.Hkv * sum(my_lens)
-    fl = 4 * w.H * w.Q * w.D * sum(my_lens) + 4 * len(my_lens) * w.H * w.Q * w.Q * w.D
+    kvb = 2 * 2 * w.D * w.Hkv * sum(my_lens) * head_share
+    fl = (4 * w.H * w.Q * w.D * sum(my_lens) + 4 * len(my_lens) * w.H * w.Q * w.Q * w.D) * head_share
     rows = env.gather([ms_stage1, float(kvb), float(fl)])
     slow = max(range(len(rows)), key=lambda r: rows[r][0])
     ms, kvb, fl = rows[slow]
@@ -426,17 +427,23 @@ def measure_batched(env, args, name, w, sample_clocks=False):
     it (all of them at N = 1) and runs the operator on them; no collective."""
     import flash_tree_attn_b200 as fta
     from flash_tree_attn_b200 import _lib
-    from flash_tree_attn_b200.dist import shard_batch
-    from flash_tree_attn_b200.workloads import draw_lengths, make_inputs, small
+    from flash_tree_attn_b200.dist import shard_batch_and_heads, take_heads
+    from flash_tree_attn_b200.workloads import draw_lengths, make_inputs
 
     lens = draw_lengths(w)
-    mine = shard_batch(lens, env.world)[env.rank] if env.world > 1 else list(range(w.B))
+    shards = shard_batch_and_heads(lens, w.Hkv, env.world)
+    mine, kv_lo, kv_hi = shards[env.rank]
+    head_share = (kv_hi - kv_lo) / w.Hkv  # 1 unless there are fewer sequences than ranks
     my_lens = [lens[i] for i in mine]
     res = {"scaling": "strong"}
     prep = inp = None
     if mine:
         inp = make_inputs(w, env.dev, lens=lens, seqs=mine)
-        ws = small(w, B=len(mine))
+        if head_share < 1:  # this rank's KV heads of its sequences, and the query heads that read them
+            for n, mul in (("q", w.G), ("k_cache", 1), ("v_cache", 1), ("current_k", 1), ("current_v", 1)):
+                inp[n] = take_heads(inp[n], kv_lo, kv_hi, mul)
+            if inp["mask"].dim() == 4 and inp["mask"].size(1) > 1:
+                inp["mask"] = take_heads(inp["mask"], kv_lo, kv_hi, w.G)
         if args.paged:
             from flash_tree_attn_b200.workloads import to_paged
             kp, vp, table = to_paged(inp["k_cache"], inp["v_cache"], my_lens, page_size=args.paged, seed=w.seed)
@@ -463,7 +470,7 @@ def measure_batched(env, args, name, w, sample_clocks=False):
     ms2 = local_loop_ms(prep.run_stage2, args.steps) if prep else 0.0
     s = env.reduce([ms1, ms2], "max")
     res["stage_ms"] = {"stage1": s[0], "stage2": s[1]}
-    res["roofline"] = stage1_roofline(env, w, name, ms1, my_lens, args)
+    res["roofline"] = stage1_roofline(env, w, name, ms1, my_lens, args, head_share)
     if sampler:
         # The timed regions last milliseconds, nvidia-smi samples every 50 ms: keep the same call
         # running (untimed) for half a second so that the clock record is one of this load.
@@ -480,7 +487,9 @@ def measure_batched(env, args, name, w, sample_clocks=False):
     res["kv_read_frac_of_nominal_8tbs"] = res["kv_read_gbs"] / (8000.0 * env.world)
     res["tflops"] = (4 * w.H * w.Q * w.D * sum(lens) + 4 * w.B * w.H * w.Q * w.Q * w.D) * res["value"] / 1e12
     res["gpu_launches_per_step"] = 2 * env.world
-    res["sequences_per_rank"] = [len(x) for x in shard_batch(lens, env.world)] if env.world > 1 else [w.B]
+    res["sequences_per_rank"] = [len(x.seqs) for x in shards]
+    if head_share < 1:
+        res["kv_heads_per_rank"] = kv_hi - kv_lo
 
     # ---- parity of what was timed -------------------------------------------------------------
     if not args.no_check and not args.paged:
@@ -500,7 +509,7 @@ def measure_batched(env, args, name, w, sample_clocks=False):
                 return fta.flash_decoding_attention(st["q"], inp["k_cache"], inp["v_cache"], st["current_k"],
                                                     st["current_v"], st["mask"], st["kv_seq_len"], w.block_size, w.ctx,
                                                     kv_group_num=w.G)
-            e2e = E2E(env, inp, (len(mine), w.H, w.Q, w.D), w.dtype, call)
+            e2e = E2E(env, inp, (len(mine), (kv_hi - kv_lo) * w.G, w.Q, w.D), w.dtype, call)
             res["e2e"] = e2e.measure(args.steps)
         else:  # a rank without sequences only keeps the barriers in step
             for _ in range(REGIONS + 1):

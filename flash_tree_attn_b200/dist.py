@@ -38,6 +38,34 @@ def shard_batch(lengths: Sequence[int], world_size: int) -> List[List[int]]:
     return [sorted(x) for x in out]
 
 
+class Shard(NamedTuple):
+    """What one rank of a batched job computes: these sequences, KV heads [kv_lo, kv_hi) of each
+    (query heads [kv_lo * kv_group_num, kv_hi * kv_group_num))."""
+    seqs: List[int]
+    kv_lo: int
+    kv_hi: int
+
+
+def shard_batch_and_heads(lengths: Sequence[int], num_kv_heads: int, world_size: int) -> List[Shard]:
+    """Batch first, then KV heads: with at least as many sequences as ranks every rank takes whole
+    sequences (`shard_batch`); with fewer, the KV heads are cut into d parts, d the smallest power
+    of two with len(lengths) * d >= world_size that divides both num_kv_heads and world_size, and the
+    sequences are dealt to world_size / d groups of d ranks.  Every (sequence, KV head) pair is
+    independent (flash_tree_attn.py:49-51,71-73), so no rank needs another's result."""
+    B = len(lengths)
+    d = 1
+    while B * d < world_size and num_kv_heads % (2 * d) == 0 and world_size % (2 * d) == 0:
+        d *= 2
+    groups = shard_batch(lengths, world_size // d)
+    per = num_kv_heads // d
+    return [Shard(groups[r // d], (r % d) * per, (r % d + 1) * per) for r in range(world_size)]
+
+
+def take_heads(t: torch.Tensor, lo: int, hi: int, mul: int = 1) -> torch.Tensor:
+    """Heads [lo * mul, hi * mul) of a [bsz, heads, ...] tensor (a view)."""
+    return t[:, lo * mul:hi * mul]
+
+
 def kv_ranges(kv_len: int, world_size: int, align: int = 64) -> List[Tuple[int, int]]:
     """Contiguous KV row ranges [lo, hi) per rank, boundaries rounded to `align` rows."""
     per = -(-kv_len // world_size)
@@ -108,7 +136,8 @@ class PeerExchange:
     `form`: "gather" (every rank reads all partials and merges all rows; the results are new
     tensors), "scatter" (every rank merges its slice of the rows and stores it into every rank's
     result buffer; the results are views of that buffer, overwritten by the next call), or
-    "auto": the gather form, the faster one where both were measured.
+    "auto": the gather form on 2 GPUs, the scatter form on 4 or more (the faster one where both were
+    measured).
     The calls `mine()` ... `merge()` must come in the same order on every rank; the object counts
     the epoch and alternates between the two partial buffers itself.
     """
@@ -127,7 +156,9 @@ class PeerExchange:
             raise ValueError(f"at most {_lib.FTA_MAX_RANKS} ranks")
         if form not in ("auto", "gather", "scatter"):
             raise ValueError(form)
-        self.scatter = form == "scatter"
+        # measured on one box (cfg4, µs per call, gather / scatter): 2 GPUs 177.5 / 181.2, 4 GPUs
+        # 118.1 / 113.8; with more ranks the gather form pulls (world - 1) whole partials per GPU
+        self.scatter = form == "scatter" or (form == "auto" and self.world >= 4)
         self.no, self.nl = int(numel_o), int(numel_lse)
         self.layout = exchange_layout(self.no, self.nl, self.world)
         self.stride = self.layout.stride

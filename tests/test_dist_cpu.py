@@ -195,3 +195,42 @@ def test_exchange_layout_is_aligned_and_disjoint():
         assert all(x % 4 == 0 for x in L)
         assert L.stride >= no + nl and L.out == 2 * L.stride
         assert L.lse >= L.out + no and L.flags >= L.lse + nl and L.total >= L.flags + 2 * world
+
+
+def test_batch_then_kv_head_shards_cover_the_job_once_and_reassemble():
+    """Sharding by batch, then by KV head when sequences run out: every (sequence, KV head) pair
+    lands on exactly one rank, and the ranks' results put side by side are the whole job's (the
+    oracle stands in for the operator)."""
+    import torch
+
+    from flash_tree_attn_b200.dist import shard_batch_and_heads, take_heads
+    from flash_tree_attn_b200.workloads import Workload, make_inputs
+    from oracle.tree_attention_oracle import tree_attention_oracle
+
+    for B, Hkv, G, world in ((8, 4, 2, 4), (2, 8, 1, 8), (3, 2, 4, 8), (1, 4, 2, 2), (5, 3, 1, 4)):
+        lens = [17 + 31 * b for b in range(B)]
+        shards = shard_batch_and_heads(lens, Hkv, world)
+        assert len(shards) == world
+        seen = {}
+        for sh in shards:
+            for b in sh.seqs:
+                for h in range(sh.kv_lo, sh.kv_hi):
+                    seen[(b, h)] = seen.get((b, h), 0) + 1
+        assert seen == {(b, h): 1 for b in range(B) for h in range(Hkv)}, (B, Hkv, world)
+
+    w = Workload("shard", 2, 8, 2, 32, 4, torch.float16, 128, "fixed:100,37", "random", seed=5)
+    inp = make_inputs(w, "cpu")
+    whole = tree_attention_oracle(inp["q"], inp["k_cache"], inp["v_cache"], inp["current_k"], inp["current_v"],
+                                  inp["mask"], inp["kv_seq_len"], None, w.G)["out"]
+    got = torch.full_like(whole, float("nan"))
+    for sh in shard_batch_and_heads(draw := [100, 37], w.Hkv, 8):
+        if not sh.seqs:
+            continue
+        part = make_inputs(w, "cpu", lens=draw, seqs=sh.seqs)
+        for n, mul in (("q", w.G), ("k_cache", 1), ("v_cache", 1), ("current_k", 1), ("current_v", 1)):
+            part[n] = take_heads(part[n], sh.kv_lo, sh.kv_hi, mul)
+        o = tree_attention_oracle(part["q"], part["k_cache"], part["v_cache"], part["current_k"], part["current_v"],
+                                  part["mask"], part["kv_seq_len"], None, w.G)["out"]
+        for i, b in enumerate(sh.seqs):
+            got[b, sh.kv_lo * w.G:sh.kv_hi * w.G] = o[i]
+    assert torch.equal(got, whole)
