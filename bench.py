@@ -702,8 +702,12 @@ def main():
         for name in PERF_CONFIGS:
             if name == args.workload:
                 continue
-            r, _ = measure(env, args, name)
-            r.pop("_lens")
+            try:
+                r, _ = measure(env, args, name)
+                r.pop("_lens")
+            except Exception as e:  # one configuration's failure must not cost the line its other numbers
+                r = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.synchronize()
             per[name] = r
 
     if env.rank == 0:
