@@ -101,10 +101,7 @@ struct FtaBalanced {
   }
 
   __host__ __device__ static int choose_per(long long total, int grid, int min_per) {
-    if (grid < 1) grid = 1;
-    long long per;
-    if (total < 0x7fffffffLL - grid) per = (long long)(((unsigned int)total + (unsigned int)grid - 1u) / (unsigned int)grid);
-    else per = (total + grid - 1) / grid;  // 64-bit division is slow on the device
+    long long per = (total + grid - 1) / (grid > 0 ? grid : 1);
     if (per < min_per) per = min_per;
     if (per < 1) per = 1;
     return (int)per;
@@ -223,23 +220,17 @@ __device__ __forceinline__ int4* fta_cut_desc(const FtaParams& p, const FtaGeom&
   return reinterpret_cast<int4*>(ws_l + (long long)2 * g.grid * g.R);
 }
 
-// Build of the prefix table pre[0..B] in shared memory by the warp whose first thread is `t0`; the
-// clamped lengths themselves go to lens_out[0..B) when it is given.  Must be followed by a barrier
-// between the building warp and whoever reads the tables.
-__device__ __forceinline__ void fta_build_prefix(const FtaParams& p, int n_tree, int pad, int* pre, int t0 = 0,
-                                                 int* lens_out = nullptr) {
-  if ((int)threadIdx.x >= t0 && (int)threadIdx.x < t0 + 32) {
-    const int lane = threadIdx.x - t0;
+// Block-cooperative build of the prefix table pre[0..B] in shared memory (warp 0 scans).
+// Must be followed by __syncthreads().
+__device__ __forceinline__ void fta_build_prefix(const FtaParams& p, int n_tree, int pad, int* pre) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
     int carry = 0;
     if (lane == 0) pre[0] = 0;
     for (int base = 0; base < p.B; base += 32) {
       const int b = base + lane;
       int v = 0;
-      if (b < p.B) {
-        const int L = fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx);
-        if (lens_out) lens_out[b] = L;
-        v = fta_unit_tiles(L, n_tree, pad);
-      }
+      if (b < p.B) v = fta_unit_tiles(fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx), n_tree, pad);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, v, o);

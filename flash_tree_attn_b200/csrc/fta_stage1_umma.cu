@@ -83,10 +83,8 @@ __host__ __device__ constexpr uint32_t col_p(bool pairs, uint32_t buf) { return 
 __host__ __device__ constexpr uint32_t col_stat(bool pairs) { return pairs ? 448u : 480u; }
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
 constexpr uint32_t kXBytes = 2 * 64 * 64 * 4 + 2 * 64 * 2 * 4;  // CS = 2: per half 64 rows x 64 unnormalised O columns, and (m, l) per row
-// with_lens: room for the lengths themselves after the prefix table (saves the planner a global read per piece)
-__host__ __device__ constexpr size_t smem_bytes(int ns, int B, int cs, bool with_lens = false) {
-  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + kSegBytes +
-         (size_t)(B + 1 + (with_lens ? B : 0)) * 4 + (cs == 2 ? 0 : 1024);
+constexpr size_t smem_bytes(int ns, int B, int cs) {
+  return (size_t)OFF_RING + (size_t)ns * kStage + (cs == 2 ? kXBytes : 0) + kBarBytes + kSegBytes + (size_t)(B + 1) * 4 + (cs == 2 ? 0 : 1024);
 }
 
 // mbarrier slots (ring barriers are sized for the largest ring)
@@ -109,17 +107,10 @@ struct Maps {
 struct Walker {
   const FtaParams& p;
   const FtaGeom& g;
-  const int* pre;
-  const int* lens;  // clamped lengths in shared memory, or null: read them from global memory
   FtaBalanced plan;
   long long lin, lin_end, item, n_items;
-  __device__ Walker(const FtaParams& p_, const FtaGeom& g_, const int* pre_, const int* lens_)
-      : p(p_), g(g_), pre(pre_), lens(lens_) {
+  __device__ Walker(const FtaParams& p_, const FtaGeom& g_, const int* pre) : p(p_), g(g_) {
     lin = lin_end = item = n_items = 0;
-  }
-  __device__ int len_of(int b) const { return lens ? lens[b] : fta_load_len(p.kv_seq_len, p.len_is_i64, b, p.ctx); }
-  // reads the prefix table: call once it is complete
-  __device__ void start() {
     if (p.split_mode == FTA_SPLIT_BALANCED) {
       plan.init(pre, p.B, g, gridDim.x);
       if (!plan.range(blockIdx.x, gridDim.x, lin, lin_end)) lin = lin_end = 0;
@@ -134,7 +125,7 @@ struct Walker {
         if (lin >= lin_end) return false;
         lin = plan.segment_at(blockIdx.x, lin, seg);
       } while (fta_seg_empty(seg));
-      const int Lb = len_of(seg.b);
+      const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, seg.b, p.ctx);
       if (seg.c1 > Lb) seg.c1 = Lb;
       return true;
     }
@@ -147,7 +138,7 @@ struct Walker {
       seg.split = (int)(r - (long long)seg.j * per_unit);
       item += gridDim.x;
       seg.nsplit = 0; seg.slot = 0;
-      const int Lb = len_of(seg.b);
+      const int Lb = fta_load_len(p.kv_seq_len, p.len_is_i64, seg.b, p.ctx);
       if (seg.split == g.fixed_max_splits) {
         if (g.n_tree == 0) continue;
         seg.c0 = seg.c1 = 0; seg.tt0 = 0; seg.tt1 = g.n_tree;
@@ -260,22 +251,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if ((r & (kR / CS - 1)) >= box_rows) reinterpret_cast<uint4*>(sm + OFF_Q)[i] = make_uint4(0, 0, 0, 0);
     }
   }
-  // The planner warp builds the tables it alone reads (prefix of tile counts, lengths) and works out
-  // the block's first piece while the others set the block up; it publishes after the barrier.
-  unsigned int dyn_smem;
-  asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_smem));
-  int* lens_s = (size_t)dyn_smem >= smem_bytes(NS, p.B, CS, true) ? pre + p.B + 1 : nullptr;  // when the launcher found room
-  Walker walker(p, g, pre, p.split_mode == FTA_SPLIT_BALANCED ? lens_s : nullptr);
-  FtaSeg seg0;
-  bool have0 = false;
-  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, g.pad, pre, 96, lens_s);
-  if (warp == 3) {
-    __syncwarp();
-    if (lane == 0) {
-      walker.start();
-      have0 = walker.next(seg0);
-    }
-  }
+  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, g.pad, pre);
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
   tc_fence_before();
   __syncthreads();
@@ -290,9 +266,10 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       // Walks this block's pieces of work once, for everybody: the lookup (a search in the prefix
       // table, divisions, a sequence length from global memory) is off every other role's path.
       if (lane == 0) {
-        FtaSeg seg = seg0;
+        Walker w(p, g, pre);
+        FtaSeg seg;
         for (uint32_t k = 0;; ++k) {
-          const bool have = k == 0 ? have0 : walker.next(seg);
+          const bool have = w.next(seg);
           const uint32_t slot = k % kSegRing;
           if (k >= kSegRing && !mbar_wait(BAR(B_SEGFREE + slot), ((k / kSegRing) - 1) & 1, abort_flag, 0x402)) break;
           SegDesc d;
@@ -1284,7 +1261,7 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
   // six ring stages when everything else leaves room for them, else five
   const int cs = g.cs == 2 ? 2 : 1;
   const int ns = smem_bytes(6, p.B, cs) <= 227 * 1024 ? 6 : 5;
-  const size_t smem = smem_bytes(ns, p.B, cs, smem_bytes(ns, p.B, cs, true) <= 227 * 1024);
+  const size_t smem = smem_bytes(ns, p.B, cs);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   void (*kern)(const FtaParams, const FtaGeom, const Maps);
   const bool f16 = p.dtype == FTA_DTYPE_F16;
