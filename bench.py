@@ -54,7 +54,7 @@ REGIONS = 5  # timed regions of K steps each; the median is reported
 # grows in proportion to the KV rows a launch streams)
 NCU_TRAFFIC_RATIO = {
     "cfg2": (1.089, "profiles/stage1_umma_cfg2.md (one full-size launch)"),
-    "cfg3": (1.043, "profiles/stage1_umma_cfg2.md (cfg3 at batch 8, scaled by KV bytes)"),
+    "cfg3": (1.046, "profiles/stage1_umma_cfg2.md (cfg3 at batch 8, scaled by KV bytes)"),
     "cfg4": (1.016, "profiles/stage1_umma_cfg2.md (one full-size launch)"),
     "cfg5": (1.011, "profiles/stage1_mma_cfg5.md (cfg5 at batch 16, scaled by KV bytes)"),
 }
