@@ -31,3 +31,35 @@ def test_product_arm_has_no_cpu_path():
     r = _run("--steps", "1", "--warmup", "3", "--no-cpu-baseline")
     assert not [ln for ln in r.stdout.splitlines() if ln.startswith("{")], "no number may be printed without a GPU"
     assert "no CPU path" in (r.stdout + r.stderr)
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_product_arm_line_carries_the_contract_keys():
+    """One short run of the GPU arm on a small batch of the headline workload: one JSON line with the
+    contract's keys, a roofline fraction that is a fraction, an end-to-end figure with its copies
+    declared, the oracle check of what was timed, and a clean kernel status."""
+    env = dict(os.environ)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--workload", "cfg3", "--batch", "4", "--only",
+                        "--steps", "3", "--warmup", "3", "--no-cpu-baseline", "--no-triton"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+              "vs_baseline", "dtype", "data", "config", "roofline", "e2e", "gpu_launches", "clocks"):
+        assert k in d, k
+    assert d["metric"] == "tree_attn_calls_per_s" and d["unit"] == "calls/s" and d["n_gpus"] == 1 and d["value"] > 0
+    assert d["config"]["workload"].startswith("cfg3") and d["dtype"] == "bf16" and d["vs_baseline"] is None
+    roof = d["roofline"]
+    assert roof["bound"] == "hbm" and roof["unit"] == "GB/s" and 0 < roof["frac"] < 1.3
+    assert abs(roof["frac"] - roof["achieved"] / roof["peak"]) < 1e-9
+    e2e = d["e2e"]
+    assert e2e["value"] > 0 and e2e["h2d_bytes_per_step"] > 0 and e2e["d2h_bytes_per_step"] > 0
+    assert e2e["value"] <= d["value"] * 1.05  # copies can only cost
+    assert d["gpu_launches"] == 2 * 3 * 5  # stage 1 + stage 2, 3 steps, 5 timed regions
+    assert d["within_tolerance"] is True and d["kernel_status"] == 0
+    assert d["max_abs_out"] <= 2e-3 + 2.0 ** -8 and d["max_abs_lse"] <= 1e-3
