@@ -53,6 +53,28 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
   if (p.split_mode == FTA_SPLIT_BALANCED) {
     const int row0 = (blockIdx.y * kRowsPerBlock + (threadIdx.x >> 5)) * kRowsPerWarp;
     if (row0 >= g.R) return;
+    const float* ws_o = reinterpret_cast<const float*>(p.workspace);
+    const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
+    // Piece 1 (and any later one) of the unit this block may have to merge sits in a slot that follows
+    // from the block index alone, so its load goes out together with the load of the cut descriptor (which says
+    // whether there is anything to merge, how many pieces, and where piece 0 is): one round trip less
+    // on a path that is nothing but round trips.  A slot read in vain is inside the workspace.
+    constexpr int kAhead = 1;  // piece 1: needed whenever there is anything to merge, so never read in vain then
+    const int c40 = lane * 4;
+    float lse_a[kRowsPerWarp][kAhead];
+    float4 o_a[kRowsPerWarp][kAhead];
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) {
+      const long long blk = (long long)blockIdx.x + (long long)k * g.lanes;
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        lse_a[r][k] = -INFINITY; o_a[r][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (blk < g.grid && row0 + r < g.R && c40 < D) {
+          lse_a[r][k] = ws_l[2 * blk * g.R + row0 + r];
+          o_a[r][k] = *reinterpret_cast<const float4*>(ws_o + (2 * blk * g.R + row0 + r) * D + c40);
+        }
+      }
+    }
     const int4 cut = fta_cut_desc(p, g)[blockIdx.x];
     const int np = cut.z;
     if (np < 2) return;
@@ -62,18 +84,31 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
     bool live[kRowsPerWarp];
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r) live[r] = row0 + r < g.R && fta_row(p, g, unit, row0 + r, h[r], qi[r]);
-    const float* ws_o = reinterpret_cast<const float*>(p.workspace);
-    const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
-    for (int c4 = lane * 4; c4 < D; c4 += 128) {
+    for (int c4 = c40; c4 < D; c4 += 128) {
       Acc acc[kRowsPerWarp];
 #pragma unroll
       for (int r = 0; r < kRowsPerWarp; ++r) acc[r].init();
-      for (int s0 = 0; s0 < np; s0 += 4) {
+      // pieces in order: 0 (from the descriptor's slot), then 1 (already here for the first 128
+      // columns), then the rest four at a time
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        if (!live[r]) continue;
+        const long long slot = cut.w;
+        acc[r].add(ws_l[slot * g.R + row0 + r], *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row0 + r) * D + c4));
+      }
+      if (c4 == c40) {
+#pragma unroll
+        for (int k = 0; k < kAhead; ++k)
+#pragma unroll
+          for (int r = 0; r < kRowsPerWarp; ++r)
+            if (live[r] && 1 + k < np) acc[r].add(lse_a[r][k], o_a[r][k]);
+      }
+      for (int s0 = c4 == c40 ? 1 + kAhead : 1; s0 < np; s0 += 4) {
         float lse[kRowsPerWarp][4]; float4 o[kRowsPerWarp][4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int s = s0 + k;
-          const long long slot = s == 0 ? (long long)cut.w : 2ll * ((long long)blockIdx.x + (long long)(s - 1) * g.lanes);
+          const long long slot = 2ll * ((long long)blockIdx.x + (long long)(s - 1) * g.lanes);
 #pragma unroll
           for (int r = 0; r < kRowsPerWarp; ++r) {
             lse[r][k] = -INFINITY; o[r][k] = make_float4(0.f, 0.f, 0.f, 0.f);
