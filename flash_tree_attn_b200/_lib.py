@@ -13,6 +13,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # FTA_LIB_PATH points at a library built elsewhere (same ABI); the default is the in-tree build.
 LIB_PATH = os.environ.get("FTA_LIB_PATH") or os.path.join(_HERE, "libfta.so")
 
+ABI_VERSION = 101  # FTA_VERSION of include/fta.h this binding was written against
+
 FTA_OK = 0
 FTA_E_BADARG = 1
 FTA_E_UNSUPPORTED = 2
@@ -138,6 +140,9 @@ def load():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
         fn.restype = res
         fn.argtypes = args
+    if lib.fta_version() != ABI_VERSION:
+        raise FtaLibraryMissing(f"{LIB_PATH} has ABI version {lib.fta_version()}, this package binds version {ABI_VERSION}: "
+                                "rebuild it with `python -m flash_tree_attn_b200.build`")
     _lib = lib
     return lib
 

@@ -29,7 +29,9 @@
 extern "C" {
 #endif
 
-#define FTA_VERSION 100
+/* 101: FtaExchangeParams.done points at two int32s (scatter form); stage 2 is a programmatic
+   dependent launch.  100: first version. */
+#define FTA_VERSION 101
 
 /* ---- error codes ------------------------------------------------------------------- */
 #define FTA_OK 0

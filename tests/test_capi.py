@@ -27,7 +27,7 @@ def test_header_symbols_exported(fta_lib):
 
 
 def test_version_and_strerror(fta_lib):
-    assert fta_lib.fta_version() == 100
+    assert fta_lib.fta_version() == 101
     assert fta_lib.fta_strerror(0) == b"ok"
     for code in range(1, 6):
         assert len(fta_lib.fta_strerror(code)) > 3
