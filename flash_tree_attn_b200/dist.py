@@ -156,8 +156,8 @@ class PeerExchange:
             raise ValueError(f"at most {_lib.FTA_MAX_RANKS} ranks")
         if form not in ("auto", "gather", "scatter"):
             raise ValueError(form)
-        # measured on one box (cfg4, µs per call, gather / scatter): 2 GPUs 177.5 / 181.2, 4 GPUs
-        # 118.1 / 113.8; with more ranks the gather form pulls (world - 1) whole partials per GPU
+        # measured on one box (one 131072-row sequence, µs per call, gather / scatter): 2 GPUs 177 / 183,
+        # 4 GPUs 118 / 115, 8 GPUs 111 / 83: the gather form pulls (world - 1) whole partials per GPU
         self.scatter = form == "scatter" or (form == "auto" and self.world >= 4)
         self.no, self.nl = int(numel_o), int(numel_lse)
         self.layout = exchange_layout(self.no, self.nl, self.world)
