@@ -63,3 +63,20 @@ def test_product_arm_line_carries_the_contract_keys():
     assert d["gpu_launches"] == 2 * 3 * 5  # stage 1 + stage 2, 3 steps, 5 timed regions
     assert d["within_tolerance"] is True and d["kernel_status"] == 0
     assert d["max_abs_out"] <= 2e-3 + 2.0 ** -8 and d["max_abs_lse"] <= 1e-3
+
+
+def test_reference_arm_under_a_multi_rank_launch():
+    """Launched as one of several ranks (torch.distributed.run exports OMP_NUM_THREADS=1): rank 0 alone
+    runs the arm, on all host cores, and says that the job is partitioned over the ranks; the other
+    ranks print nothing and exit 0."""
+    base = dict(os.environ, CUDA_VISIBLE_DEVICES="", WORLD_SIZE="4", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "cfg1", "--gpus", "4",
+           "--steps", "3", "--warmup", "3"]
+    r1 = subprocess.run(cmd, capture_output=True, text=True, env=dict(base, RANK="1"), timeout=600)
+    assert r1.returncode == 0 and not [ln for ln in r1.stdout.splitlines() if ln.startswith("{")]
+    r0 = subprocess.run(cmd, capture_output=True, text=True, env=dict(base, RANK="0"), timeout=600)
+    assert r0.returncode == 0, r0.stderr
+    d = json.loads([ln for ln in r0.stdout.splitlines() if ln.startswith("{")][-1])
+    assert d["impl"] == "reference" and d["n_gpus"] == 4 and d["scaling"] == "strong"
+    assert d["cpu_baseline"]["cores"] == (os.cpu_count() or 1)
+    assert "4 GPUs" in d["config"]["parallelism"]
