@@ -181,14 +181,20 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
     const T* ckbase = CKp + seg.b * p.ck_sb + (long long)unit.kvh * p.cur_head_mul * p.ck_sh;
     const T* cvbase = CVp + seg.b * p.cv_sb + (long long)unit.kvh * p.cur_head_mul * p.cv_sh;
 
-    auto issue_tile = [&](int i) {
+    // where cache tile i starts (paged cache: a block-table read); asked one tile ahead of its use,
+    // so that no copy is issued behind a table read
+    auto tile_at = [&](int i) {
+      FtaTileAt at = {0, 0};
+      if (i < n_ct) at = fta_tile_at(p, seg.b, seg.c0 + i * FTA_TILE);
+      return at;
+    };
+    auto issue_tile = [&](int i, const FtaTileAt& at) {
       if (i < n_tiles) {
         const uint32_t sK = sBody_a + (i % C::STAGES) * C::STAGE_BYTES;
         const uint32_t sV = sK + FTA_TILE * C::ROWB;
         if (i < n_ct) {
           const int row0 = seg.c0 + i * FTA_TILE;
           const int valid = seg.c1 - row0 < FTA_TILE ? seg.c1 - row0 : FTA_TILE;
-          const FtaTileAt at = fta_tile_at(p, seg.b, row0);
           load_rows<T, D>(sK, kbase + at.batch * p.k_sb + (long long)at.row * p.k_st, p.k_st, valid);
           load_rows<T, D>(sV, vbase + at.batch * p.v_sb + (long long)at.row * p.v_st, p.v_st, valid);
         } else {
@@ -209,8 +215,14 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
       const T* src = ok ? Qp + seg.b * p.q_sb + h * p.q_sh + qi * p.q_sq + ch * 8 : Qp;
       cp_async16(sQ_a + row * C::ROWB + (swz<C::CH>(row, ch) << 4), src, ok ? 16 : 0);
     }
+    {
+      FtaTileAt first[C::STAGES - 1];
 #pragma unroll
-    for (int i = 0; i < C::STAGES - 1; ++i) issue_tile(i);
+      for (int i = 0; i < C::STAGES - 1; ++i) first[i] = tile_at(i);  // the reads go out together
+#pragma unroll
+      for (int i = 0; i < C::STAGES - 1; ++i) issue_tile(i, first[i]);
+    }
+    FtaTileAt at_next = tile_at(C::STAGES - 1);
 
     uint32_t qf[C::Q_IN_REGS ? D / 16 : 1][4];
     float acc_o[D / 8][4];
@@ -222,7 +234,8 @@ stage1_kernel(const FtaParams p, const FtaGeom g) {
     for (int i = 0; i < n_tiles; ++i) {
       cp_async_wait<C::STAGES - 2>();
       __syncthreads();
-      issue_tile(i + C::STAGES - 1);
+      issue_tile(i + C::STAGES - 1, at_next);
+      at_next = tile_at(i + C::STAGES);
 
       if (C::Q_IN_REGS && i == 0) {
 #pragma unroll

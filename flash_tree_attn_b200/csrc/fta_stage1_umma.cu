@@ -310,7 +310,14 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           // first K tiles of a piece are requested before its Q tile: they do not depend on the
           // Q buffer having been handed back, so they overlap the previous piece's tail.  (The
           // block's first piece has no predecessor and the first S waits for Q: there Q leads.)
+          // Paged cache: a tile's page comes from the block table.  The entry for tile u + 1 is
+          // requested while tile u is being issued, and a tile's entry is kept for its V copy two
+          // iterations later, so that no copy waits for a table read.
+          FtaTileAt at_m2 = {0, 0}, at_m1 = {0, 0}, at_0 = {0, 0}, at_p1 = {0, 0};  // tiles u - 2, u - 1, u, u + 1
+          if (n_ct > 0) at_0 = fta_tile_at(p, seg.b, seg.c0);
           for (int u = 0; u < n + 2 && ok; ++u) {
+            if (u > 0) { at_m2 = at_m1; at_m1 = at_0; at_0 = at_p1; }
+            if (u + 1 < n_ct) at_p1 = fta_tile_at(p, seg.b, seg.c0 + (u + 1) * FTA_TILE);
             if (u == q_at) {
               ok = mbar_wait(BAR(B_QEMPTY), (sidx & 1) ^ 1, abort_flag, 0x101);
               if (!ok) break;
@@ -330,7 +337,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
               const CUtensorMap* m;
               int row0, head, bidx = seg.b;
               if (i < n_ct) {
-                const FtaTileAt at = fta_tile_at(p, seg.b, seg.c0 + i * FTA_TILE);  // dense: (b, row); paged: (page, row in page)
+                const FtaTileAt at = which == 0 ? at_0 : at_m2;  // dense: (b, row); paged: (page, row in page)
                 m = which == 0 ? &maps.k : &maps.v; row0 = at.row; bidx = at.batch; head = seg.kvh;
               } else { m = which == 0 ? &maps.ck : &maps.cv; row0 = (seg.tt0 + i - n_ct) * FTA_TILE; head = seg.kvh * p.cur_head_mul; }
               const uint32_t full = BAR((which == 0 ? B_KFULL : B_VFULL) + st);
