@@ -13,9 +13,9 @@ cudaError_t fta_launch_stage1_mma_d32(const FtaParams&, const FtaGeom&, cudaStre
 cudaError_t fta_launch_stage1_mma_d64(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*);
 cudaError_t fta_launch_stage1_mma_d128(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*);
 cudaError_t fta_launch_stage1_mma_d256(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*);
-cudaError_t fta_launch_stage1_umma(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*);
+cudaError_t fta_launch_stage1_umma(const FtaParams&, const FtaGeom&, cudaStream_t, int, int*, int overlap);
 int fta_umma_supported(const FtaParams&);
-cudaError_t fta_launch_stage2(const FtaParams&, const FtaGeom&, cudaStream_t);
+cudaError_t fta_launch_stage2(const FtaParams&, const FtaGeom&, cudaStream_t, int overlap);
 cudaError_t fta_launch_commit(const FtaCommitParams&, cudaStream_t);
 cudaError_t fta_launch_merge_parts(const FtaMergeParams&, cudaStream_t);
 cudaError_t fta_launch_exchange_merge(const FtaExchangeParams&, cudaStream_t);
@@ -177,7 +177,7 @@ int make_geom(const FtaParams& p, FtaGeom& g, bool need_grid) {
   int& occ = g_occ[dev & 15][fam == FTA_KERNEL_UMMA][p.dtype][d_index(p.D)][r_index(g.R)][kb < 33 ? kb : 33];
   if (occ == 0) {
     int o = 0;
-    cudaError_t e = fam == FTA_KERNEL_UMMA ? fta_launch_stage1_umma(p, g, 0, 1, &o) : launch_mma(p, g, 0, 1, &o);
+    cudaError_t e = fam == FTA_KERNEL_UMMA ? fta_launch_stage1_umma(p, g, 0, 1, &o, 0) : launch_mma(p, g, 0, 1, &o);
     if (e != cudaSuccess) return cuda_fail(e);
     if (o < 1) return FTA_E_UNSUPPORTED;
     occ = o;
@@ -192,9 +192,12 @@ int64_t ws_bytes(const FtaParams& p, const FtaGeom& g) {
   return (int64_t)2 * g.grid * g.R * (p.D + 1) * 4 + (int64_t)g.grid * 16;
 }
 
-int run_stage1(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
+// overlap: the two stages are launched with programmatic stream serialization, so that each grid is
+// set up while the kernel before it in the stream drains (a whole call); 0 = ordinary launches (a
+// stage run alone, e.g. to be timed).
+int run_stage1(const FtaParams& p, const FtaGeom& g, cudaStream_t st, int overlap) {
   if (p.split_mode == FTA_SPLIT_BALANCED && p.workspace_bytes < ws_bytes(p, g)) return FTA_E_WORKSPACE;
-  cudaError_t e = g.family == FTA_KERNEL_UMMA ? fta_launch_stage1_umma(p, g, st, 0, nullptr)
+  cudaError_t e = g.family == FTA_KERNEL_UMMA ? fta_launch_stage1_umma(p, g, st, 0, nullptr, overlap)
                                             : launch_mma(p, g, st, 0, nullptr);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
@@ -242,7 +245,7 @@ int fta_stage1(const FtaParams* p, void* stream) {
   FtaGeom g;
   rc = make_geom(*p, g, true);
   if (rc) return rc;
-  return run_stage1(*p, g, (cudaStream_t)stream);
+  return run_stage1(*p, g, (cudaStream_t)stream, 0);
 }
 
 int fta_stage2(const FtaParams* p, void* stream) {
@@ -251,7 +254,7 @@ int fta_stage2(const FtaParams* p, void* stream) {
   FtaGeom g;
   rc = make_geom(*p, g, true);
   if (rc) return rc;
-  cudaError_t e = fta_launch_stage2(*p, g, (cudaStream_t)stream);
+  cudaError_t e = fta_launch_stage2(*p, g, (cudaStream_t)stream, 0);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 
@@ -261,9 +264,9 @@ int fta_decode(const FtaParams* p, void* stream) {
   FtaGeom g;
   rc = make_geom(*p, g, true);
   if (rc) return rc;
-  rc = run_stage1(*p, g, (cudaStream_t)stream);
+  rc = run_stage1(*p, g, (cudaStream_t)stream, 1);
   if (rc) return rc;
-  cudaError_t e = fta_launch_stage2(*p, g, (cudaStream_t)stream);
+  cudaError_t e = fta_launch_stage2(*p, g, (cudaStream_t)stream, 1);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 
@@ -293,9 +296,9 @@ int fta_decode_static(const FtaParams* p, void* stream) {
   rc = make_geom(q, g, true);
   if (rc) return rc;
   if (ws_bytes(q, g) > (int64_t)FTA_STATIC_SCRATCH_BYTES) return FTA_E_TOO_LARGE;
-  rc = run_stage1(q, g, (cudaStream_t)stream);
+  rc = run_stage1(q, g, (cudaStream_t)stream, 1);
   if (rc) return rc;
-  e = fta_launch_stage2(q, g, (cudaStream_t)stream);
+  e = fta_launch_stage2(q, g, (cudaStream_t)stream, 1);
   return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 

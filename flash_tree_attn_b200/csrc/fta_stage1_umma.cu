@@ -251,8 +251,12 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if ((r & (kR / CS - 1)) >= box_rows) reinterpret_cast<uint4*>(sm + OFF_Q)[i] = make_uint4(0, 0, 0, 0);
     }
   }
-  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, g.pad, pre);
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  // Everything above is local to the block.  If this grid was launched to overlap the kernel before it
+  // in the stream, that kernel (and whatever it waited for) has finished once this returns; nothing in
+  // global memory is read or written before.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (p.split_mode == FTA_SPLIT_BALANCED) fta_build_prefix(p, g.n_tree, g.pad, pre);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1264,7 +1268,7 @@ int fta_umma_supported(const FtaParams& p) {
 }
 
 cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStream_t st, int query_only,
-                                   int* blocks_per_sm) {
+                                   int* blocks_per_sm, int overlap) {
   // six ring stages when everything else leaves room for them, else five
   const int cs = g.cs == 2 ? 2 : 1;
   const int ns = smem_bytes(6, p.B, cs) <= 227 * 1024 ? 6 : 5;
@@ -1315,8 +1319,18 @@ cudaError_t fta_launch_stage1_umma(const FtaParams& p, const FtaGeom& g, cudaStr
     maps.cv = maps.v;
   }
   if (!ok) return cudaErrorInvalidValue;
-  kern<<<g.grid, kThreads, smem, st>>>(p, g, maps);
-  return cudaGetLastError();
+  // overlap: with programmatic stream serialization the blocks are placed and set themselves up
+  // (barriers, tensor memory, descriptors) while the kernel before this one in the stream drains, if
+  // that kernel allows it (the previous call's stage 2 does); they touch global memory only after
+  // griddepcontrol.wait.  After any other kernel the launch behaves like an ordinary one.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(g.grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cfg.attrs = attr; cfg.numAttrs = overlap ? 1 : 0;
+  const cudaError_t e2 = cudaLaunchKernelEx(&cfg, kern, p, g, maps);
+  return e2 != cudaSuccess ? e2 : cudaGetLastError();
 }
 
 #ifdef FTA_UMMA_PROFILE

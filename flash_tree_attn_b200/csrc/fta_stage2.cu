@@ -38,7 +38,13 @@ constexpr int kRowsPerBlock = kThreads / 32;
 // Waits until the kernel launched before this one on the stream (stage 1) has completed and its
 // stores are visible.  Stage 2 is launched with programmatic stream serialization, so its blocks are
 // set up while stage 1 still runs and start the moment it has finished.
-__device__ __forceinline__ void wait_for_stage1() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Also lets a kernel that follows in the stream and was launched the same way (the next call's stage 1)
+// be set up now; it reads and writes nothing before its own griddepcontrol.wait, which returns once
+// this grid, and so the stage 1 it waited for, has finished.
+__device__ __forceinline__ void wait_for_stage1() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // One warp per query row (two rows per warp in the BALANCED plan), one float4 of head_dim per lane (two
 // for head_dim 256).  Loads of up to four partials per row are issued before any is folded in.
@@ -371,7 +377,7 @@ cudaError_t fta_launch_exchange_merge(const FtaExchangeParams& p, cudaStream_t s
   return cudaGetLastError();
 }
 
-cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st) {
+cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t st, int overlap) {
   const bool balanced = p.split_mode == FTA_SPLIT_BALANCED;
   // rows past hpt * qpt of a unit's tile are padding: no blocks for them
   const int rows = g.hpt * g.qpt < g.R ? g.hpt * g.qpt : g.R;
@@ -384,7 +390,7 @@ cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = overlap ? 1 : 0;  // 0: an ordinary launch (the stage is being timed alone)
   cudaError_t e = cudaLaunchKernelEx(&cfg, stage2_kernel, p, g);
   if (e != cudaSuccess) return e;
   if (balanced && !p.with_tree) {

@@ -262,7 +262,11 @@ int64_t fta_workspace_bytes(const FtaParams* p);
 /*
  * The whole operator: stage 1 (split-KV partial attention with the tree-masked tail
  * fused in) and stage 2 (LSE merge), replacing flash_tree_attn.py:301-376.
- * `stream` is a cudaStream_t.
+ * `stream` is a cudaStream_t.  Both kernels are launched with programmatic stream
+ * serialization and allow the kernel after them in the stream to be set up early: a
+ * kernel the caller launches behind this call WITH that same attribute must, as the
+ * attribute's contract says, wait for its grid dependency (cudaGridDependencySynchronize)
+ * before it reads `out` / `lse`; an ordinary launch needs nothing.
  */
 int fta_decode(const FtaParams* p, void* stream);
 
