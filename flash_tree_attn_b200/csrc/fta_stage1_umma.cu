@@ -13,14 +13,17 @@
 //               tensor pipe with 12 small products per tile and answer five barriers in time
 //   warp 3      planner: walks the block's pieces of work once and hands each to the other roles
 //               as a 64-byte descriptor in a shared-memory ring
-//   warps 4..7  softmax: a thread owns one row (TMEM lane): copies its Q row into TMEM at the
-//               start of a piece; per tile tcgen05.ld of S, scale, tree mask / sequence-end
-//               mask, running max with lazy rescale of O, exp2 (half of them on the FMA pipe),
-//               P (16-bit pairs) stored to TMEM; at the end of a piece the row's maximum and sum
-//               go to the epilogue warps through two TMEM columns and the next piece starts
-//   warps 8..11 epilogue: read a finished piece's O rows from TMEM (handing the accumulator back at
-//               once), normalise, stage through the Q buffer and store 256-byte row pieces, and the
-//               LSE; all of it beside the next piece's tiles
+//   warps 4..7  softmax: a thread owns one row (TMEM lane); per tile tcgen05.ld of S, scale, tree
+//               mask / sequence-end mask, running max with lazy rescale of O, exp2 (half of them on
+//               the FMA pipe), P (16-bit pairs) stored to TMEM over the S columns just read; at the
+//               end of a piece the row's maximum and sum go to the epilogue warps through two TMEM
+//               columns and the next piece starts (with two Q buffers its first S tiles are waiting)
+//   warps 8..11 epilogue: a thread owns one row; where TMEM has room for two Q buffers (no tile
+//               pairs, no column split) it copies the Q row of the NEXT piece from shared memory into
+//               the other buffer while the current piece is worked on (else the softmax thread copies
+//               it at the start of the piece); reads a finished piece's O rows from TMEM (handing the
+//               accumulator back at once), normalises, stages through the Q buffer and stores 256-byte
+//               row pieces, and the LSE; all of it beside the next piece's tiles
 //
 // Registers are rebalanced with setmaxnreg (64 per thread for warps 0..3, 240 for the softmax, 200
 // for the epilogue).
@@ -65,21 +68,29 @@ constexpr uint32_t OFF_RING = OFF_Q + kQBytes;
 constexpr uint32_t kBarBytes = 512;
 constexpr int kSegRing = 8;                  // pieces of work the planner may run ahead
 constexpr uint32_t kSegBytes = kSegRing * 64;
-// TMEM columns (32-bit).  Several S buffers let S = Q K^T run ahead of the softmax; a P buffer is
-// not overwritten before the product that read it, PV(t - buffers), is complete, and S(t) is not
-// issued before that either, so neither wait is on the softmax's path.
-//   three buffers:  O fp32 0..127 | S fp32 128 + 64 k (k < 3) | Q 16-bit pairs 320..383 | P 16-bit
-//                   pairs 384 + 32 k | row statistics 480..481.
+// TMEM columns (32-bit).  Several S buffers let S = Q K^T run ahead of the softmax.  A thread has
+// all of its S row in registers before it writes P, so P(t) (16-bit pairs) goes over the first 32
+// columns of S(t); S(t) is not issued before PV(t - buffers), which read that P, is complete.
+//   three buffers:  O fp32 0..127 | S/P 128 + 64 k (k < 3) | Q of even pieces 320..383 | Q of odd
+//                   pieces 384..447 | row statistics 480..481.  With two Q buffers the next piece's Q
+//                   rows are in TMEM long before the piece starts, so its first products are issued
+//                   behind the last ones of the piece before and S never runs dry at a boundary.
+//   three buffers, column split (CS = 2):  O 0..127 | S 128 + 64 k | Q 320..383 (one buffer) | P
+//                   384 + 32 k, apart from S: the half of a P row that belongs to the other half of
+//                   the tile's rows is zeroed once and never written again | statistics 480..481.
 //   four buffers (template PAIRS, where the softmax takes full tiles two at a time):  O 0..127 |
-//                   S/P 128 + 64 k (k < 4): a thread has all of its S row in registers before it
-//                   writes P, so P(t) goes over the first 32 columns of S(t) | Q 384..447 | row
+//                   S/P 128 + 64 k (k < 4) | Q 384..447 (one buffer: no room for two) | row
 //                   statistics 448..449.
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxBuf = 4;
 __host__ __device__ constexpr int n_buf(bool pairs) { return pairs ? 4 : 3; }
 constexpr uint32_t kColS = 128;  // + 64 * buffer
-__host__ __device__ constexpr uint32_t col_q(bool pairs) { return pairs ? 384u : 320u; }  // 64 columns: 128 head-dim elements, two per column
-__host__ __device__ constexpr uint32_t col_p(bool pairs, uint32_t buf) { return pairs ? kColS + 64u * buf : 384u + 32u * buf; }
+__host__ __device__ constexpr int n_qbuf(bool pairs, int cs) { return (pairs || cs == 2) ? 1 : 2; }
+// 64 columns per buffer: 128 head-dim elements, two per column
+__host__ __device__ constexpr uint32_t col_q(bool pairs, int cs, uint32_t piece) {
+  return pairs ? 384u : 320u + (cs == 2 ? 0u : 64u * (piece & 1u));
+}
+__host__ __device__ constexpr uint32_t col_p(bool, int cs, uint32_t buf) { return cs == 2 ? 384u + 32u * buf : kColS + 64u * buf; }
 __host__ __device__ constexpr uint32_t col_stat(bool pairs) { return pairs ? 448u : 480u; }
 // shared-memory size of a block with NS ring stages and a B-entry prefix table
 constexpr uint32_t kXBytes = 2 * 64 * 64 * 4 + 2 * 64 * 2 * 4;  // CS = 2: per half 64 rows x 64 unnormalised O columns, and (m, l) per row
@@ -89,7 +100,7 @@ constexpr size_t smem_bytes(int ns, int B, int cs) {
 
 // mbarrier slots (ring barriers are sized for the largest ring)
 constexpr int kMaxNS = 6;
-enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
+enum { B_QFULL = 0, B_QEMPTY, B_QREADY, B_ODONE = B_QREADY + 2, B_OFREE = B_ODONE + 4, B_KFULL, B_VFULL = B_KFULL + kMaxNS,
        B_KEMPTY = B_VFULL + kMaxNS, B_VEMPTY = B_KEMPTY + kMaxNS, B_SFULL = B_VEMPTY + kMaxNS, B_PREADY = B_SFULL + kMaxBuf,
        B_FINAL = B_PREADY + kMaxBuf, B_XFULL = B_FINAL + 2, B_XFREE, B_SEGFULL, B_SEGFREE = B_SEGFULL + kSegRing,
        B_STATS = B_SEGFREE + kSegRing, B_STATSFREE, B_COUNT };
@@ -189,7 +200,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   constexpr uint32_t OFF_SEG = OFF_BAR + kBarBytes;
   static_assert(!(PAIRS && CS == 2), "tiles are taken in pairs only without the column split");
   constexpr int kNBuf = n_buf(PAIRS);
-  constexpr uint32_t kColQ = col_q(PAIRS), kColStat = col_stat(PAIRS);
+  constexpr uint32_t kColStat = col_stat(PAIRS);
+  constexpr int kQBuf = n_qbuf(PAIRS, CS);
   constexpr uint32_t OFF_PRE = OFF_SEG + kSegBytes;
   // Swizzle atoms are 1024-byte aligned.  Without the column split there is room to round the base
   // up; with it every kilobyte is taken, the declared alignment is relied on and checked.
@@ -210,6 +222,9 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_BAR + kBarBytes - 4);
   const uint32_t bar0 = base + OFF_BAR;
 #define BAR(i) (bar0 + 8u * (uint32_t)(i))
+  // Q(piece) is announced on one barrier per TMEM buffer, so that a waiter can never be two phases behind
+  auto qready_bar = [&](uint32_t piece) -> uint32_t { return BAR(B_QREADY + (kQBuf == 2 ? (piece & 1u) : 0u)); };
+  auto qready_par = [&](uint32_t piece) -> uint32_t { return (kQBuf == 2 ? (piece >> 1) : piece) & 1u; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef FTA_UMMA_PROFILE
@@ -233,7 +248,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   // one barrier per thread: slot i expects count(i) arrivals per phase
   if (tid < B_COUNT) {
     uint32_t count = 1;
-    if (tid == B_QEMPTY || tid == B_QREADY || tid == B_OFREE || tid == B_STATS || tid == B_STATSFREE ||
+    if (tid == B_QEMPTY || tid == B_QREADY || tid == B_QREADY + 1 || tid == B_OFREE || tid == B_STATS || tid == B_STATSFREE ||
         (tid >= B_PREADY && tid < B_PREADY + kNBuf))
       count = 128;
     else if (tid == B_XFULL || tid == B_XFREE) count = 128;
@@ -262,6 +277,32 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   if (tid == 0) FTA_TRACE_EP(12, 0);
+
+  // Q row of a thread (row = its TMEM lane): shared memory (TMA, swizzled) -> TMEM, 16-bit pairs, one
+  // per column.  One Q buffer: the softmax warps do it at the start of a piece, when every S = Q K^T of
+  // the piece before is complete (its last S has been read).  Two Q buffers: the epilogue warps do it,
+  // because they are idle while a piece's tiles are worked on, so the next piece's rows are in place
+  // well before that piece's first product is due; the buffer they write was last read by the products
+  // of the piece before the current one, which they have seen complete.
+  auto q_to_tmem = [&](int row, uint32_t t_lane, uint32_t piece) -> bool {
+    if (!wait_all(BAR(B_QFULL), piece & 1, abort_flag, 0x306)) return false;
+    if (row == 0 && piece == 0) FTA_TRACE_EP(12, 4);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t qr[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sm + OFF_Q + hf * kQHalf + row * 128 + ((c ^ (row & 7)) << 4));
+        qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
+      }
+      tmem_st32(t_lane + col_q(PAIRS, CS, piece) + 32 * hf, reinterpret_cast<const float*>(qr));
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    mbar_arrive(qready_bar(piece));
+    if (row == 0 && piece == 0) FTA_TRACE_EP(12, 5);
+    return true;
+  };
 
   if (warp < 4) {
     reg_dec<kRegsIssue>();
@@ -372,7 +413,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         seg_copy(seg, &segq[sidx % kSegRing]);
         if (!seg.valid) break;
         const int n = seg_cache_tiles(seg) + seg.tt1 - seg.tt0;
-        ok = wait_all(BAR(B_QREADY), sidx & 1, abort_flag, 0x201);  // Q rows are in TMEM
+        ok = wait_all(qready_bar(sidx), qready_par(sidx), abort_flag, 0x201);  // Q rows are in TMEM
+        const uint32_t q_tmem = tmem + col_q(PAIRS, CS, sidx);
         if (lane == 0 && sidx == 0) FTA_TRACE_EP(12, 6);
         if (lane == 0 && sidx > 0) FTA_TRACE_EP(sidx - 1, 5);
         for (int i = 0; i < n && ok; ++i) {
@@ -396,7 +438,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
             for (int ks = 0; ks < kD / 16; ++ks) {
               const uint32_t half = ks >> 2, off = (ks & 3) * 32;
-              umma_f16_ts(d_tmem, tmem + kColQ + ks * 8, dK + (uint64_t)((half * kKVHalf + off) >> 4), idesc_qk, ks > 0);
+              umma_f16_ts(d_tmem, q_tmem + ks * 8, dK + (uint64_t)((half * kKVHalf + off) >> 4), idesc_qk, ks > 0);
             }
             umma_commit(BAR(B_KEMPTY + st));
             umma_commit(BAR(B_SFULL + sbuf));
@@ -440,7 +482,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
             const uint64_t dV = dV0 + (uint64_t)((st * kStage) >> 4);
 #pragma unroll
             for (int kk = 0; kk < FTA_TILE / 16; ++kk)
-              umma_f16_ts(tmem, tmem + col_p(PAIRS, sbuf) + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
+              umma_f16_ts(tmem, tmem + col_p(PAIRS, CS, sbuf) + kk * 8, dV + (uint64_t)((kk * 16 * 128) >> 4), idesc_pv,
                           (i > 0 || kk > 0) ? 1u : 0u);
             umma_commit(BAR(B_VEMPTY + st));
             umma_commit(BAR(B_ODONE + (t & 3)));
@@ -470,7 +512,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
       for (int k = 0; k < 16; ++k) z[k] = 0u;
 #pragma unroll
-      for (int k = 0; k < kNBuf; ++k) tmem_st16(t_lane + col_p(PAIRS, k) + 16 * (chalf ^ 1), z);
+      for (int k = 0; k < kNBuf; ++k) tmem_st16(t_lane + col_p(PAIRS, CS, k) + 16 * (chalf ^ 1), z);
       tmem_st_wait();
       tc_fence_before();
     }
@@ -478,27 +520,6 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     uint32_t gt = 0, sidx = 0;
     bool ok = true;
 
-    // Q row of this thread: shared memory (TMA, swizzled) -> TMEM, 16-bit pairs, one per column.
-    // Every S = Q K^T of the previous piece is complete when this runs (its last S has been read).
-    auto q_to_tmem = [&](uint32_t piece) -> bool {
-      if (!wait_all(BAR(B_QFULL), piece & 1, abort_flag, 0x306)) return false;
-      if (row == 0 && piece == 0) FTA_TRACE_EP(12, 4);
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t qr[32];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = *reinterpret_cast<const uint4*>(sm + OFF_Q + hf * kQHalf + row * 128 + ((c ^ (row & 7)) << 4));
-          qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
-        }
-        tmem_st32(t_lane + kColQ + 32 * hf, reinterpret_cast<const float*>(qr));
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(BAR(B_QREADY));
-      if (row == 0 && piece == 0) FTA_TRACE_EP(12, 5);
-      return true;
-    };
     // V rows past the end of the sequence are zeroed so that 0 * padding cannot give NaN
     auto zero_v_tail = [&](uint32_t t, int valid) -> bool {
       const uint32_t st = t % NS;
@@ -517,7 +538,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     ok = wait_all(BAR(B_SEGFULL), 0, abort_flag, 0x300);
     if (ok) {
       seg_copy(seg, &segq[0]);
-      if (seg.valid) ok = q_to_tmem(0);
+      if (kQBuf == 1 && seg.valid) ok = q_to_tmem(row, t_lane, 0);
     } else {
       seg.valid = 0;
     }
@@ -621,7 +642,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
               }
               const uint32_t sbh = half == 0 ? sbuf : sb1;
               if (row == 0) FTA_TRACE(half == 0 ? t : t1, 4);
-              tmem_st32(t_lane + col_p(PAIRS, sbh), reinterpret_cast<const float*>(pk));  // over the S columns just read
+              tmem_st32(t_lane + col_p(PAIRS, CS, sbh), reinterpret_cast<const float*>(pk));  // over the S columns just read
               tmem_st_wait();
               tc_fence_before();
               mbar_arrive(BAR(B_PREADY + sbh));
@@ -750,8 +771,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
           l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
           // P[t%3] was the A operand of PV(t-3), which completed before S(t) was even issued
           if (row == 0) FTA_TRACE(t, 4);
-          if (CS == 2) tmem_st16(t_lane + col_p(PAIRS, sbuf) + 16 * chalf, pk);
-          else tmem_st32(t_lane + col_p(PAIRS, sbuf), reinterpret_cast<const float*>(pk));  // over the S columns just read
+          if (CS == 2) tmem_st16(t_lane + col_p(PAIRS, CS, sbuf) + 16 * chalf, pk);
+          else tmem_st32(t_lane + col_p(PAIRS, CS, sbuf), reinterpret_cast<const float*>(pk));  // over the S columns just read
           if (!is_tree && valid < FTA_TILE) {
             ok = zero_v_tail(t, valid);
             if (!ok) break;
@@ -779,7 +800,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       if (!ok) break;
       seg_copy(seg, &segq[sidx % kSegRing]);
       if (row == 0) FTA_TRACE_EP(sidx - 1, 1);
-      if (seg.valid) ok = q_to_tmem(sidx);
+      if (kQBuf == 1 && seg.valid) ok = q_to_tmem(row, t_lane, sidx);
       if (row == 0) FTA_TRACE_EP(sidx - 1, 2);
     }
     if (row == 0) {
@@ -811,7 +832,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
     else seg.valid = 0;
     if (ok && seg.valid) {
       // the Q buffer goes back to the producer, for the second piece's Q, once the first is in TMEM
-      ok = wait_all(BAR(B_QREADY), 0, abort_flag, 0x501);
+      if (kQBuf == 2) ok = q_to_tmem(row, t_lane, 0);
+      else ok = wait_all(qready_bar(0), qready_par(0), abort_flag, 0x501);
       if (ok) mbar_arrive(BAR(B_QEMPTY));
     }
     while (ok && seg.valid) {
@@ -825,6 +847,12 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
       ok = wait_all(BAR(B_SEGFULL + (sidx + 1) % kSegRing), ((sidx + 1) / kSegRing) & 1, abort_flag, 0x500);
       if (!ok) break;
       seg_copy(nseg, &segq[(sidx + 1) % kSegRing]);
+      // two Q buffers: the next piece's Q goes to TMEM as soon as it has landed, while this piece's
+      // tiles are still being worked on
+      if (kQBuf == 2 && nseg.valid) {
+        ok = q_to_tmem(row, t_lane, sidx + 1);
+        if (!ok) break;
+      }
 
       // the row's maximum and sum, as the softmax thread of the same row left them
       ok = wait_all(BAR(B_STATS), sidx & 1, abort_flag, 0x502);
@@ -843,8 +871,8 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 
       if (!working) {
         mbar_arrive(BAR(B_OFREE));
-        if (nseg.valid) {
-          ok = wait_all(BAR(B_QREADY), (sidx + 1) & 1, abort_flag, 0x503);
+        if (kQBuf == 1 && nseg.valid) {
+          ok = wait_all(qready_bar(sidx + 1), qready_par(sidx + 1), abort_flag, 0x503);
           if (!ok) break;
         }
         if (CS == 2) {  // keep the halves' exchange barriers in step
@@ -865,9 +893,9 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
         mbar_arrive(BAR(B_OFREE));
         if (row == 0) FTA_TRACE_EP(sidx, 4);
         // The Q buffer is this piece's staging area, but only after the next piece's Q, which has
-        // been sitting in it, went to TMEM.
-        if (nseg.valid) {
-          ok = wait_all(BAR(B_QREADY), (sidx + 1) & 1, abort_flag, 0x503);
+        // been sitting in it, went to TMEM (two Q buffers: that happened above).
+        if (kQBuf == 1 && nseg.valid) {
+          ok = wait_all(qready_bar(sidx + 1), qready_par(sidx + 1), abort_flag, 0x503);
           if (!ok) break;
         }
         constexpr int NCOL = CS == 2 ? 64 : kD;   // output columns this thread stores
