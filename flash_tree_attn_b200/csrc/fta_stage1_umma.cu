@@ -14,7 +14,7 @@
 //   warp 3      planner: walks the block's pieces of work once and hands each to the other roles
 //               as a 64-byte descriptor in a shared-memory ring
 //   warps 4..7  softmax: a thread owns one row (TMEM lane); per tile tcgen05.ld of S, scale, tree
-//               mask / sequence-end mask, running max with lazy rescale of O, exp2 (half of them on
+//               mask / sequence-end mask, running max with lazy rescale of O, exp2 (a quarter of them on
 //               the FMA pipe), P (16-bit pairs) stored to TMEM over the S columns just read; at the
 //               end of a piece the row's maximum and sum go to the epilogue warps through two TMEM
 //               columns and the next piece starts (with two Q buffers its first S tiles are waiting)
@@ -635,7 +635,7 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
               for (int c2 = 0; c2 < 32; ++c2) {
                 const float2 e = ffma2(make_float2(sv[2 * c2], sv[2 * c2 + 1]), make_float2(scale2, scale2), make_float2(nsub, nsub));
                 float p0, p1;
-                if (c2 & 1) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
+                if ((c2 & 3) == 3) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
                 else { p0 = fta_exp2(e.x); p1 = fta_exp2(e.y); }
                 ps[c2 & 3] += p0 + p1;
                 pk[c2] = FtaType<T>::pack(p0, p1);
@@ -760,10 +760,10 @@ stage1_umma_kernel(const FtaParams p, const FtaGeom g, const __grid_constant__ M
 #pragma unroll
           for (int c2 = 0; c2 < NC / 2; ++c2) {
             const float2 e = ffma2(make_float2(s[2 * c2], s[2 * c2 + 1]), make_float2(mul, mul), make_float2(nsub, nsub));
-            // every other pair is exponentiated on the FMA pipe, so that the MUFU (4 lanes per
-            // clock) and the FMA pipe work side by side
+            // every fourth pair is exponentiated on the FMA pipe, so that the MUFU (4 lanes per
+            // clock) and the FMA pipe work side by side (measured: a quarter beats a half by 1-3 %)
             float p0, p1;
-            if (c2 & 1) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
+            if ((c2 & 3) == 3) { const float2 y = exp2_poly2(e); p0 = y.x; p1 = y.y; }
             else { p0 = fta_exp2(e.x); p1 = fta_exp2(e.y); }
             ps[c2 & 3] += p0 + p1;
             pk[c2] = FtaType<T>::pack(p0, p1);
