@@ -273,8 +273,12 @@ def timed_regions(env, fn, steps, regions=REGIONS):
     return statistics.median(ms), ms
 
 
-def local_loop_ms(fn, steps):
-    """ms per call of `steps` back-to-back calls on this rank (CUDA events)."""
+def local_loop_ms(fn, steps, rest_s=0.25):
+    """ms per call of `steps` back-to-back calls on this rank (CUDA events).  A kernel timed alone is
+    compared with the burst peak, so the GPU first rests for `rest_s`: after the timed regions' tens of
+    milliseconds of load the power management holds the SM clock down for a while (1965 -> ~1550 MHz)."""
+    torch.cuda.synchronize()
+    time.sleep(rest_s)
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
