@@ -148,8 +148,12 @@ struct FtaBalanced {
     if (s.tt1 < s.tt0) s.tt1 = s.tt0;
     s.split = c - cfirst;
     s.nsplit = clast - cfirst + 1;
-    s.slot = 2 * cphys + (lin == cbeg ? 0 : 1);
-    s.p0slot = 2 * (cfirst * lanes + lane) + (ustart == (I)cfirst * (I)per ? 0 : 1);
+    // A block holds at most two pieces of cut units: the one that opens its range (a later piece of
+    // its unit: slot 0) and the one that closes it (the first piece of its unit: slot 1).  So every
+    // piece's slot follows from the block that holds the unit's second piece, and stage 2 can ask for
+    // the first two pieces before it has read the descriptor of the cut.
+    s.slot = 2 * cphys + (c == cfirst ? 1 : 0);
+    s.p0slot = 2 * (cfirst * lanes + lane) + 1;
     return (long long)send;
   }
   __host__ __device__ long long segment_at(int c, long long lin, FtaSeg& s) const {
@@ -212,7 +216,8 @@ __host__ __device__ __forceinline__ bool fta_row(const FtaParams& p, const FtaGe
 
 // BALANCED workspace: partial O rows [2*grid][R][D] fp32, partial LSEs [2*grid][R] fp32, then one
 // int4 per stage-1 block: the unit whose SECOND piece opens that block, {b, j, pieces, slot of the
-// first piece}, or pieces = 0.  Piece i >= 1 sits in slot 2*(block of the second piece + (i - 1)*lanes).
+// first piece}, or pieces = 0.  Piece i >= 1 sits in slot 2*(block of the second piece + (i - 1)*lanes),
+// piece 0 in slot 2*(block of the second piece - lanes) + 1.
 // Stage 2 launches one group of blocks per stage-1 block and merges exactly the units that were cut.
 __device__ __forceinline__ int4* fta_cut_desc(const FtaParams& p, const FtaGeom& g) {
   float* ws_o = reinterpret_cast<float*>(p.workspace);

@@ -51,7 +51,7 @@ __device__ __forceinline__ void wait_for_stage1() {
 //   BALANCED: grid = (stage-1 blocks, row groups): block c merges the unit whose second piece
 //             opens stage-1 block c, if any (fta_cut_desc); uncut units were finished by stage 1.
 //   FIXED:    grid = (units, row groups).
-__global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, const FtaGeom g) {
+__global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, const FtaGeom g, const int ask_first) {
   const int lane = threadIdx.x & 31;
   const int D = p.D;
   wait_for_stage1();
@@ -61,23 +61,27 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
     if (row0 >= g.R) return;
     const float* ws_o = reinterpret_cast<const float*>(p.workspace);
     const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
-    // Piece 1 (and any later one) of the unit this block may have to merge sits in a slot that follows
-    // from the block index alone, so its load goes out together with the load of the cut descriptor (which says
-    // whether there is anything to merge, how many pieces, and where piece 0 is): one round trip less
-    // on a path that is nothing but round trips.  A slot read in vain is inside the workspace.
-    constexpr int kAhead = 1;  // piece 1: needed whenever there is anything to merge, so never read in vain then
+    // Every piece of the unit this block may have to merge sits in a slot that follows from the block
+    // index alone (piece 0: slot 1 of the block before this one's group neighbour, piece i >= 1: slot 0
+    // of block + (i - 1) * lanes), so the loads of pieces 0 and 1 go out together with the load of the
+    // cut descriptor (which says whether there is anything to merge and how many pieces): a round trip
+    // less on a path that is nothing but round trips.  A slot read in vain is inside the workspace.
+    // Piece 1's slot is this block's own and is always asked for; piece 0's only where most blocks
+    // do merge (ask_first: at least as many units as blocks, so a unit is cut once at most) - with few
+    // long units most blocks open with a third or later piece and would read it in vain.
+    constexpr int kAhead = 2;  // pieces 0 and 1: both needed whenever there is anything to merge
     const int c40 = lane * 4;
     float lse_a[kRowsPerWarp][kAhead];
     float4 o_a[kRowsPerWarp][kAhead];
 #pragma unroll
     for (int k = 0; k < kAhead; ++k) {
-      const long long blk = (long long)blockIdx.x + (long long)k * g.lanes;
+      const long long slot = k == 0 ? 2ll * ((long long)blockIdx.x - g.lanes) + 1 : 2ll * (long long)blockIdx.x;
 #pragma unroll
       for (int r = 0; r < kRowsPerWarp; ++r) {
         lse_a[r][k] = -INFINITY; o_a[r][k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (blk < g.grid && row0 + r < g.R && c40 < D) {
-          lse_a[r][k] = ws_l[2 * blk * g.R + row0 + r];
-          o_a[r][k] = *reinterpret_cast<const float4*>(ws_o + (2 * blk * g.R + row0 + r) * D + c40);
+        if (slot >= 0 && (k > 0 || ask_first) && row0 + r < g.R && c40 < D) {
+          lse_a[r][k] = ws_l[slot * g.R + row0 + r];
+          o_a[r][k] = *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row0 + r) * D + c40);
         }
       }
     }
@@ -94,22 +98,27 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
       Acc acc[kRowsPerWarp];
 #pragma unroll
       for (int r = 0; r < kRowsPerWarp; ++r) acc[r].init();
-      // pieces in order: 0 (from the descriptor's slot), then 1 (already here for the first 128
-      // columns), then the rest four at a time
-#pragma unroll
-      for (int r = 0; r < kRowsPerWarp; ++r) {
-        if (!live[r]) continue;
-        const long long slot = cut.w;
-        acc[r].add(ws_l[slot * g.R + row0 + r], *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row0 + r) * D + c4));
-      }
-      if (c4 == c40) {
+      // pieces in order: 0 and 1 (already here for the first 128 columns), then the rest four at a time
+      if (c4 == c40 && ask_first) {
 #pragma unroll
         for (int k = 0; k < kAhead; ++k)
 #pragma unroll
           for (int r = 0; r < kRowsPerWarp; ++r)
-            if (live[r] && 1 + k < np) acc[r].add(lse_a[r][k], o_a[r][k]);
+            if (live[r]) acc[r].add(lse_a[r][k], o_a[r][k]);
+      } else {
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+          if (!live[r]) continue;
+          const long long slot = cut.w;
+          acc[r].add(ws_l[slot * g.R + row0 + r], *reinterpret_cast<const float4*>(ws_o + (slot * g.R + row0 + r) * D + c4));
+        }
+        if (c4 == c40) {
+#pragma unroll
+          for (int r = 0; r < kRowsPerWarp; ++r)
+            if (live[r]) acc[r].add(lse_a[r][1], o_a[r][1]);
+        }
       }
-      for (int s0 = c4 == c40 ? 1 + kAhead : 1; s0 < np; s0 += 4) {
+      for (int s0 = c4 == c40 ? kAhead : 1; s0 < np; s0 += 4) {
         float lse[kRowsPerWarp][4]; float4 o[kRowsPerWarp][4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -391,7 +400,9 @@ cudaError_t fta_launch_stage2(const FtaParams& p, const FtaGeom& g, cudaStream_t
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
   cfg.attrs = attr; cfg.numAttrs = overlap ? 1 : 0;  // 0: an ordinary launch (the stage is being timed alone)
-  cudaError_t e = cudaLaunchKernelEx(&cfg, stage2_kernel, p, g);
+  // units on the line against groups of blocks that share it
+  const int ask_first = balanced && (long long)p.B * g.U >= (long long)g.grid ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, stage2_kernel, p, g, ask_first);
   if (e != cudaSuccess) return e;
   if (balanced && !p.with_tree) {
     cfg.gridDim = dim3(p.B);
