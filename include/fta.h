@@ -286,7 +286,8 @@ int fta_decode(const FtaParams* p, void* stream);
  *  - The first call on a device looks up the array's device address (no allocation); make that
  *    first call with the device current and before any stream capture begins.
  *  - All calls on a device share the one array and it keeps whatever the last call left there.
- *    Nothing in it has to start at zero: stage 1 writes every slot stage 2 reads.  Two calls
+ *    Nothing in it has to start at zero: stage 1 writes every slot stage 2 uses (stage 2 may load
+ *    a slot before it knows whether it is needed, and then drops it).  Two calls
  *    whose kernels overlap on the GPU (different streams) race on it; serialise them.
  *  - Neither this function nor anything it calls uses cudaMalloc, cudaFree or an allocating
  *    library routine.
