@@ -200,6 +200,8 @@ def test_balanced_plan_covers_every_tile_once(fta_lib, seed):
     assert len(seen_cache) == sum(lens) * U
     # balance: no block gets more than `per` tiles
     assert max(per_block.values()) <= per
+    mtiles = U // Hkv  # M tiles of one KV head walk the same range in neighbouring blocks ("lanes")
+    _check_slot_rule(rows, lanes=mtiles if (mtiles > 1 and grid >= mtiles) else 1)
 
 
 def test_plan_is_balanced_for_ragged_batch(fta_lib):
@@ -225,3 +227,30 @@ def test_plan_is_balanced_for_ragged_batch(fta_lib):
         if (packed & 0xFFFF) > 1:
             cut[c] = cut.get(c, 0) + 1
     assert max(cut.values()) <= 2
+    _check_slot_rule(rows)
+
+
+def _check_slot_rule(rows, lanes=1):
+    """A cut unit's first piece goes to slot 1 of its block and every later piece to slot 0 (stage 2
+    finds all of them from the index of the block that holds the second piece), so a block must
+    never hold two first pieces or two later pieces, a unit's pieces must sit in consecutive groups
+    of blocks, and the second piece must open its block."""
+    first, later, where = {}, {}, {}
+    seen_in_block = {}
+    for (c, b, j, c0, c1, t0, t1, packed) in rows:
+        split, nsplit = packed >> 16, packed & 0xFFFF
+        seen_in_block.setdefault(c, []).append((b, j, split, nsplit))
+        if nsplit < 2:
+            continue
+        if split == 0:
+            first[c] = first.get(c, 0) + 1
+        else:
+            later[c] = later.get(c, 0) + 1
+        where[(b, j, split)] = c
+    assert all(v == 1 for v in first.values()) and all(v == 1 for v in later.values())
+    for (b, j, split), c in where.items():
+        if split > 0:
+            assert where[(b, j, split - 1)] == c - lanes, "pieces of a unit sit in consecutive blocks"
+            assert seen_in_block[c][0][:3] == (b, j, split), "a later piece opens its block"
+        else:
+            assert seen_in_block[c][-1][:3] == (b, j, 0), "a first piece closes its block"
