@@ -152,6 +152,26 @@ def test_many_short_sequences(fta, B, Q, G, kernel):
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("B,Q,G,Hkv,long_len", [(40, 26, 4, 4, 30000), (160, 64, 1, 1, 20000), (150, 4, 1, 2, 24000)])
+def test_one_long_sequence_among_many_short_ones(fta, B, Q, G, Hkv, long_len, kernel):
+    """As many units as stage-1 blocks or more, so the merge asks for a cut unit's first two pieces
+    before it has read the cut's descriptor, while one sequence is long enough for its units to be
+    cut into many pieces: pieces 2.. come after the descriptor, in the same order."""
+    from flash_tree_attn_b200.workloads import make_inputs
+    import random
+
+    fta.set_kernel(kernel)
+    rng = random.Random(B + Q)
+    lens = [rng.choice([1, 30, 64, 65, 100, 130]) for _ in range(B)]
+    lens[B // 3] = long_len
+    ctx = -(-long_len // 64) * 64
+    w = _workload(B=B, H=Hkv * G, G=G, D=128, Q=Q, ctx=ctx, lens="fixed:" + ",".join(map(str, lens)))
+    inp = make_inputs(w, "cuda")
+    out, lse = _run(fta, inp, G, ctx=ctx)
+    _check(out, lse, _oracle(inp, G), f"B={B} Q={Q} G={G} long={long_len}")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("page_size", [64, 128])
 @pytest.mark.parametrize("shape", [(3, 4, 1, 128, 4, 512, "fixed:16,500,129"), (2, 8, 4, 128, 26, 1024, "fixed:1000,333"),
                                    (2, 4, 1, 128, 64, 1024, "fixed:1024,0"), (2, 4, 2, 64, 16, 256, "fixed:255,64")])
