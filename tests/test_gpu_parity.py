@@ -450,3 +450,32 @@ def test_call_is_capturable_in_a_cuda_graph_and_follows_the_lengths(fta):
         graph.replay()
         torch.cuda.synchronize()
         _check(out, lse, _oracle(inp, 2), f"graph replay lens={lens}")
+
+
+def test_two_calls_in_one_cuda_graph(fta):
+    """Two calls captured back to back: the second call's stage 1 is a programmatic dependent of the
+    first call's stage 2 inside the graph (its set-up overlaps that kernel's drain), and the two
+    calls share the library's workspace, so the second must not touch it before the first is done."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel("auto")
+    wa = _workload(B=4, H=8, G=2, D=128, Q=32, ctx=4096, lens="fixed:4096,900,3,2500", seed=5)
+    wb = _workload(B=4, H=8, G=2, D=128, Q=32, ctx=4096, lens="fixed:70,4000,1234,64", seed=6)
+    ia, ib = make_inputs(wa, "cuda"), make_inputs(wb, "cuda")
+
+    def args(i):
+        return (i["q"], i["k_cache"], i["v_cache"], i["current_k"], i["current_v"], i["mask"], i["kv_seq_len"], 64, 4096)
+
+    fta.prepare(*args(ia), kv_group_num=2, want_lse=True).run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        oa, la = fta.prepare(*args(ia), kv_group_num=2, want_lse=True).run()
+        ob, lb = fta.prepare(*args(ib), kv_group_num=2, want_lse=True).run()
+    for rep in range(3):
+        ia["q"].normal_()
+        ib["q"].normal_()
+        graph.replay()
+        torch.cuda.synchronize()
+        _check(oa, la, _oracle(ia, 2), f"first call, replay {rep}")
+        _check(ob, lb, _oracle(ib, 2), f"second call, replay {rep}")
