@@ -479,3 +479,30 @@ def test_two_calls_in_one_cuda_graph(fta):
         torch.cuda.synchronize()
         _check(oa, la, _oracle(ia, 2), f"first call, replay {rep}")
         _check(ob, lb, _oracle(ib, 2), f"second call, replay {rep}")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_alternating_calls_share_the_workspace(fta, kernel):
+    """Two different jobs issued alternately, hundreds of times, without a synchronisation between
+    them: a call's stage 1 is set up while the previous call's stage 2 is still reading the partial
+    results that both keep in the same workspace, and must not write there before that is over."""
+    from flash_tree_attn_b200.workloads import make_inputs
+
+    fta.set_kernel(kernel)
+    wa = _workload(B=6, H=8, G=2, D=128, Q=32, ctx=8192, lens="fixed:8192,900,3,2500,7000,64", seed=7)
+    wb = _workload(B=6, H=8, G=2, D=128, Q=32, ctx=8192, lens="fixed:70,8000,1234,64,1,5000", seed=8)
+    ia, ib = make_inputs(wa, "cuda"), make_inputs(wb, "cuda")
+
+    def prep(i):
+        return fta.prepare(i["q"], i["k_cache"], i["v_cache"], i["current_k"], i["current_v"], i["mask"],
+                           i["kv_seq_len"], 64, 8192, kv_group_num=2, want_lse=True)
+
+    pa, pb = prep(ia), prep(ib)
+    ref_a, ref_b = _oracle(ia, 2), _oracle(ib, 2)
+    for rep in range(3):
+        for _ in range(100):
+            oa, la = pa.run()
+            ob, lb = pb.run()
+        torch.cuda.synchronize()
+        _check(oa, la, ref_a, f"job A after round {rep}")
+        _check(ob, lb, ref_b, f"job B after round {rep}")
