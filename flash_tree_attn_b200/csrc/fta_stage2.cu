@@ -62,10 +62,11 @@ __global__ void __launch_bounds__(kThreads) stage2_kernel(const FtaParams p, con
     const float* ws_o = reinterpret_cast<const float*>(p.workspace);
     const float* ws_l = ws_o + (long long)2 * g.grid * g.R * D;
     // Every piece of the unit this block may have to merge sits in a slot that follows from the block
-    // index alone (piece 0: slot 1 of the block before this one's group neighbour, piece i >= 1: slot 0
-    // of block + (i - 1) * lanes), so the loads of pieces 0 and 1 go out together with the load of the
-    // cut descriptor (which says whether there is anything to merge and how many pieces): a round trip
-    // less on a path that is nothing but round trips.  A slot read in vain is inside the workspace.
+    // index alone (piece 0: slot 1 of block - lanes, the block that walked the range before this one's
+    // for the same M tile; piece i >= 1: slot 0 of block + (i - 1) * lanes), so the loads of pieces 0
+    // and 1 go out together with the load of the cut descriptor (which says whether there is anything
+    // to merge and how many pieces): a round trip less on a path that is nothing but round trips.  A
+    // slot read in vain is inside the workspace.
     // Piece 1's slot is this block's own and is always asked for; piece 0's only where most blocks
     // do merge (ask_first: at least as many units as blocks, so a unit is cut once at most) - with few
     // long units most blocks open with a third or later piece and would read it in vain.
